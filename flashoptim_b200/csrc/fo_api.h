@@ -1,0 +1,94 @@
+// C ABI of libflashoptim_b200.so.  Every function returns a cudaError_t value
+// (0 on success) unless stated otherwise, takes raw device pointers and a CUDA
+// stream handle, launches asynchronously on that stream and allocates nothing.
+#pragma once
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Element type codes.
+enum FoDtype { FO_BF16 = 0, FO_FP16 = 1, FO_FP32 = 2 };
+
+// One tensor of a multi-tensor launch.  64 bytes.
+//   p     parameter, updated in place
+//   g     gradient, same dtype and length as p
+//   ecc   error-correction codes (int8 or int16, same length) or null
+//   s0    first state: int8 codes when quantised, else param dtype; momentum /
+//         exp_avg; null when the optimizer keeps no state
+//   s0s   fp16 scales of s0, one per 32 elements (quantised only)
+//   s1    second state (Adam exp_avg_sq): uint8 codes or param dtype
+//   s1s   fp16 scales of s1
+//   n     number of elements
+typedef struct FoSeg {
+  void* p;
+  const void* g;
+  void* ecc;
+  void* s0;
+  void* s0s;
+  void* s1;
+  void* s1s;
+  int64_t n;
+} FoSeg;
+
+typedef struct FoAdamHyper {
+  float lr, beta1, beta2, eps;
+  float weight_decay;  // already folded: wd*lr (decoupled) or wd (coupled)
+  float rbc1, rbc2;    // 1 / (1 - beta^step)
+  float grad_scale;    // gradient is multiplied by this before use
+  int decoupled;
+} FoAdamHyper;
+
+typedef struct FoMomentumHyper {
+  float lr;
+  float mom_coef;      // SGD momentum | Lion beta2
+  float update_coef;   // SGD 1 - dampening | Lion beta1
+  float weight_decay;  // folded like FoAdamHyper.weight_decay
+  float grad_scale;
+  int lion, nesterov, decoupled;
+} FoMomentumHyper;
+
+// State storage of the momentum family.
+enum FoStateMode { FO_STATE_NONE = 0, FO_STATE_Q8 = 1, FO_STATE_FULL = 2 };
+
+enum { FO_MAX_INLINE_SEGS = 16 };
+
+// Elements covered by one CTA iteration ("chunk").  Segment s occupies chunks
+// [chunk_begin[s], chunk_begin[s+1]) with chunk_begin[s+1] - chunk_begin[s] =
+// ceil(n_s / fo_chunk_elems()).
+int fo_chunk_elems(void);
+// Number of CTAs the step kernels are launched with on `device` (<= total chunks).
+int fo_step_grid(int device);
+
+// Multi-tensor fused steps.  `segs` / `chunk_begin` are HOST pointers when
+// n_seg <= FO_MAX_INLINE_SEGS and `table_on_device` is 0 (the table then
+// travels in the kernel parameters, no device memory is touched), DEVICE
+// pointers otherwise.  total_chunks = chunk_begin[n_seg].
+int fo_adam_step(const FoSeg* segs, const int32_t* chunk_begin, int n_seg, int total_chunks,
+                 int table_on_device, int dtype, int err_bytes, int quantized, const FoAdamHyper* hyper,
+                 void* stream);
+int fo_momentum_step(const FoSeg* segs, const int32_t* chunk_begin, int n_seg, int total_chunks,
+                     int table_on_device, int dtype, int err_bytes, int state_mode,
+                     const FoMomentumHyper* hyper, void* stream);
+
+// Group quantiser and its inverse (exact IEEE arithmetic; see ops/oracle.py).
+// `x` has element type `dtype`; `q` int8 (signed) or uint8; `scales` fp16.
+int fo_quantize(const void* x, int dtype, void* q, void* scales, int64_t n, int is_signed, int do_sqrt,
+                int softsign, void* stream);
+int fo_dequantize(const void* q, const void* scales, float* out, int64_t n, int is_signed, int do_sqrt,
+                  int softsign, void* stream);
+
+// Master-weight split: narrow (bf16/fp16) + int8/int16 codes <-> fp32 (exact).
+int fo_ecc_decode(const void* narrow, int dtype, const void* ecc, int err_bytes, float* out, int64_t n,
+                  void* stream);
+int fo_ecc_encode(const float* x, const void* narrow, int dtype, void* ecc, int err_bytes, int64_t n,
+                  void* stream);
+
+// max |x| of a tensor, accumulated into *out (a float the caller zeroed).
+int fo_maxabs(const void* x, int dtype, int64_t n, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,183 @@
+"""Launch wrappers of the fused multi-tensor optimizer steps.
+
+A launch takes a list of "segments" (one per tensor: parameter, gradient,
+correction codes, state tensors, length) and updates all of them with one
+kernel.  Up to 16 segments travel inside the kernel parameters; longer lists
+live in a small device-resident table that is re-uploaded only when one of the
+addresses changed since the previous step (with PyTorch's caching allocator
+gradients come back at the same addresses step after step, so in steady state
+nothing is uploaded).  The reference launches one Triton kernel per tensor
+(``flashoptim/optimizers.py:1535-1579``, ``:2203-2251``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import native
+
+SEG_WORDS = 8  # int64 words per segment: p, g, ecc, s0, s0s, s1, s1s, n
+
+
+@dataclass
+class AdamHyper:
+    lr: float
+    beta1: float
+    beta2: float
+    eps: float
+    weight_decay: float  # folded: wd*lr (decoupled) or wd (coupled)
+    step: int
+    decoupled: bool
+    grad_scale: float = 1.0
+
+    def to_c(self) -> native.FoAdamHyper:
+        from .oracle import bias_corrections
+
+        rbc1, rbc2 = bias_corrections(self.beta1, self.beta2, self.step)
+        return native.FoAdamHyper(
+            self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, rbc1, rbc2,
+            self.grad_scale, int(self.decoupled),
+        )
+
+
+@dataclass
+class MomentumHyper:
+    lr: float
+    mom_coef: float
+    update_coef: float
+    weight_decay: float
+    lion: bool = False
+    nesterov: bool = False
+    decoupled: bool = False
+    grad_scale: float = 1.0
+
+    def to_c(self) -> native.FoMomentumHyper:
+        return native.FoMomentumHyper(
+            self.lr, self.mom_coef, self.update_coef, self.weight_decay, self.grad_scale,
+            int(self.lion), int(self.nesterov), int(self.decoupled),
+        )
+
+
+class SegmentTable:
+    """Host image + (for long lists) device copy of one launch's segment table."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._host: Optional[np.ndarray] = None       # [n_seg, 8] int64, last uploaded image
+        self._chunks: Optional[np.ndarray] = None     # [n_seg + 1] int32
+        self._dev: Optional[torch.Tensor] = None      # uint8 device buffer: segs then chunk_begin
+        self.uploads = 0
+
+    @staticmethod
+    def chunk_prefix(numels: np.ndarray, chunk: int) -> np.ndarray:
+        cb = np.zeros(len(numels) + 1, dtype=np.int64)
+        np.cumsum((numels + chunk - 1) // chunk, out=cb[1:])
+        if cb[-1] >= 2**31:
+            raise ValueError("too many elements for one multi-tensor launch")
+        return cb.astype(np.int32)
+
+    def prepare(self, rows: np.ndarray) -> tuple[int, int, int, int, int]:
+        """``rows``: [n_seg, 8] int64.  Returns (segs_ptr, chunks_ptr, n_seg, total_chunks, on_device)."""
+        n_seg = rows.shape[0]
+        chunk = native.chunk_elems()
+        same_shape = self._host is not None and self._host.shape == rows.shape
+        if not same_shape or not np.array_equal(self._host[:, 7], rows[:, 7]):
+            self._chunks = self.chunk_prefix(rows[:, 7], chunk)
+            changed = True
+        else:
+            changed = not np.array_equal(self._host, rows)
+        total = int(self._chunks[-1])
+        if n_seg <= native.FO_MAX_INLINE_SEGS:
+            self._host = rows
+            return rows.ctypes.data, self._chunks.ctypes.data, n_seg, total, 0
+        if changed or self._dev is None:
+            seg_bytes = n_seg * SEG_WORDS * 8
+            img = np.empty(seg_bytes + (n_seg + 1) * 4, dtype=np.uint8)
+            img[:seg_bytes] = rows.reshape(-1).view(np.uint8)
+            img[seg_bytes:] = self._chunks.view(np.uint8)
+            staged = torch.from_numpy(img).pin_memory()
+            if self._dev is None or self._dev.numel() != img.size:
+                self._dev = torch.empty(img.size, dtype=torch.uint8, device=self.device)
+            self._dev.copy_(staged, non_blocking=True)
+            self._host = rows.copy()
+            self.uploads += 1
+        base = self._dev.data_ptr()
+        return base, base + n_seg * SEG_WORDS * 8, n_seg, total, 1
+
+
+def launch_adam(
+    table: SegmentTable,
+    rows: np.ndarray,
+    dtype: torch.dtype,
+    err_bytes: int,
+    quantized: bool,
+    hyper: AdamHyper,
+) -> None:
+    """One fused Adam/AdamW step over every segment of ``rows`` on the current stream."""
+    if rows.shape[0] == 0:
+        return
+    lib = native.load()
+    segs, chunks, n_seg, total, on_dev = table.prepare(rows)
+    h = hyper.to_c()
+    with torch.cuda.device(table.device):
+        rc = lib.fo_adam_step(
+            segs, chunks, n_seg, total, on_dev, native.DTYPE_CODE[dtype], err_bytes, int(quantized),
+            ctypes.byref(h), native.stream_ptr(table.device),
+        )
+    native.check(rc, "fo_adam_step")
+
+
+def launch_momentum(
+    table: SegmentTable,
+    rows: np.ndarray,
+    dtype: torch.dtype,
+    err_bytes: int,
+    state_mode: int,
+    hyper: MomentumHyper,
+) -> None:
+    """One fused Lion / SGD / SGDW step over every segment of ``rows``."""
+    if rows.shape[0] == 0:
+        return
+    lib = native.load()
+    segs, chunks, n_seg, total, on_dev = table.prepare(rows)
+    h = hyper.to_c()
+    with torch.cuda.device(table.device):
+        rc = lib.fo_momentum_step(
+            segs, chunks, n_seg, total, on_dev, native.DTYPE_CODE[dtype], err_bytes, state_mode,
+            ctypes.byref(h), native.stream_ptr(table.device),
+        )
+    native.check(rc, "fo_momentum_step")
+
+
+def make_rows(
+    params: Sequence[torch.Tensor],
+    grads: Sequence[torch.Tensor],
+    eccs: Sequence[Optional[torch.Tensor]],
+    s0: Sequence[Optional[torch.Tensor]],
+    s0s: Sequence[Optional[torch.Tensor]],
+    s1: Sequence[Optional[torch.Tensor]],
+    s1s: Sequence[Optional[torch.Tensor]],
+) -> np.ndarray:
+    """Pack tensor addresses into the [n_seg, 8] int64 image the kernels read."""
+    n = len(params)
+    rows = np.zeros((n, SEG_WORDS), dtype=np.int64)
+    if n == 0:
+        return rows
+
+    def ptrs(ts):
+        return [0 if t is None else t.data_ptr() for t in ts]
+
+    rows[:, 0] = ptrs(params)
+    rows[:, 1] = ptrs(grads)
+    rows[:, 2] = ptrs(eccs)
+    rows[:, 3] = ptrs(s0)
+    rows[:, 4] = ptrs(s0s)
+    rows[:, 5] = ptrs(s1)
+    rows[:, 6] = ptrs(s1s)
+    rows[:, 7] = [p.numel() for p in params]
+    return rows
