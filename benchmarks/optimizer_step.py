@@ -1,0 +1,134 @@
+"""Optimizer-step micro-benchmark on one GPU, no model.
+
+Tensors have the shapes of a Llama-3-8B parameter list (291 tensors, 8.03 B
+elements): embedding and lm_head 128256x4096; per layer (x32) q/o 4096x4096,
+k/v 1024x4096, gate/up 14336x4096, down 4096x14336 and two RMSNorm weights of
+4096.  Params ~ N(0, 0.02), grads ~ N(0, 1e-3), seed 0.  Every step reads and
+writes far more than the 126 MB L2, so no flush is needed between iterations.
+
+    python benchmarks/optimizer_step.py --optimizers adamw,lion,sgdw --mwb 24,32,none
+    python benchmarks/optimizer_step.py --impl reference   # the reference's Triton build
+
+Prints one JSON line per (optimizer, master_weight_bits): device-timed ms per
+step (CUDA events around K steps), ms per 1e9 parameters, bytes per element and
+the achieved fraction of the measured copy bandwidth (MEASURED_PEAKS.json).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def llama8b_shapes(layers: int = 32, d: int = 4096, ffn: int = 14336, vocab: int = 128256, kv: int = 1024):
+    shapes = [(vocab, d)]
+    for _ in range(layers):
+        shapes += [(d, d), (kv, d), (kv, d), (d, d), (ffn, d), (ffn, d), (d, ffn), (d,), (d,)]
+    shapes += [(d,), (vocab, d)]
+    return shapes
+
+
+def bytes_per_elem(opt: str, mwb) -> float:
+    """HBM bytes per element of one fused step: bf16 param + grad read, param write,
+    8-bit states read + written with one fp16 scale per 32 elements, codes read + written."""
+    states = 2 if opt.startswith("adam") else 1
+    ecc = {None: 0, 24: 1, 32: 2}[mwb]
+    return 2 + 2 + 2 + states * 2 * (1 + 2 / 32) + 2 * ecc
+
+
+def hbm_peak_gbs() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_optimizer(impl: str, name: str, params, mwb):
+    if impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import flashoptim as lib
+    else:
+        import flashoptim_b200 as lib
+    if name == "adamw":
+        return lib.FlashAdamW(params, lr=1e-3, betas=(0.9, 0.999), weight_decay=0.01, master_weight_bits=mwb)
+    if name == "lion":
+        return lib.FlashLion(params, lr=1e-4, betas=(0.9, 0.99), weight_decay=0.01, master_weight_bits=mwb)
+    if name == "sgdw":
+        return lib.FlashSGDW(params, lr=1e-3, momentum=0.9, weight_decay=0.01, master_weight_bits=mwb)
+    raise ValueError(name)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--optimizers", default="adamw,lion,sgdw")
+    ap.add_argument("--mwb", default="24,32,none")
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=32, help="fewer layers = smaller problem (profiling)")
+    ap.add_argument("--vocab", type=int, default=128256, help="smaller vocabulary = smaller problem")
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak, peak_src = hbm_peak_gbs()
+    shapes = llama8b_shapes(layers=args.layers, vocab=args.vocab)
+    g = torch.Generator(device=dev).manual_seed(0)
+    params = []
+    for s in shapes:
+        p = torch.empty(s, device=dev, dtype=torch.bfloat16)
+        p.copy_(torch.randn(s, device=dev, generator=g) * 0.02) if len(s) == 1 else p.normal_(0, 0.02, generator=g)
+        params.append(torch.nn.Parameter(p))
+    for p in params:
+        p.grad = torch.empty_like(p).normal_(0, 1e-3, generator=g)
+    n_total = sum(p.numel() for p in params)
+    results = []
+    import warnings
+
+    warnings.simplefilter("ignore")
+    for name in args.optimizers.split(","):
+        for m in args.mwb.split(","):
+            mwb = None if m == "none" else int(m)
+            opt = make_optimizer(args.impl, name, params, mwb)
+            for _ in range(args.warmup):
+                opt.step()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            e0.record()
+            for _ in range(args.steps):
+                opt.step()
+            e1.record()
+            host_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            bpe = bytes_per_elem(name, mwb)
+            gbs = n_total * bpe / (ms * 1e-3) / 1e9
+            rec = {
+                "impl": args.impl, "optimizer": name, "master_weight_bits": mwb, "n_tensors": len(params),
+                "n_params": n_total, "ms_per_step": round(ms, 4), "host_ms_per_step": round(host_ms, 4),
+                "ms_per_1B_params": round(ms / (n_total / 1e9), 4), "bytes_per_elem": bpe,
+                "achieved_GBps": round(gbs, 1), "hbm_peak_GBps": peak,
+                "frac_of_" + peak_src: round(gbs / peak, 4), "steps": args.steps, "warmup": args.warmup,
+            }
+            print(json.dumps(rec), flush=True)
+            results.append(rec)
+            del opt
+            torch.cuda.empty_cache()
+    if args.out:
+        with open(args.out, "w") as f:
+            for r in results:
+                f.write(json.dumps(r) + "\n")
+
+
+if __name__ == "__main__":
+    main()

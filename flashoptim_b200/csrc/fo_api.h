@@ -33,19 +33,27 @@ typedef struct FoSeg {
   int64_t n;
 } FoSeg;
 
+// Complements (1 - beta, 1 - weight_decay) are evaluated by the host in double
+// precision: 1.0f - 0.999f is off by 1.3e-5 relative.
 typedef struct FoAdamHyper {
   float lr, beta1, beta2, eps;
+  float one_minus_beta1, one_minus_beta2;
   float weight_decay;  // already folded: wd*lr (decoupled) or wd (coupled)
-  float rbc1, rbc2;    // 1 / (1 - beta^step)
+  float decay;         // 1 - weight_decay when decoupled, else 1
+  float rbc1;          // 1 / (1 - beta1^step)
+  float sqrt_rbc2;     // sqrt(1 / (1 - beta2^step))
   float grad_scale;    // gradient is multiplied by this before use
   int decoupled;
 } FoAdamHyper;
 
 typedef struct FoMomentumHyper {
   float lr;
-  float mom_coef;      // SGD momentum | Lion beta2
-  float update_coef;   // SGD 1 - dampening | Lion beta1
-  float weight_decay;  // folded like FoAdamHyper.weight_decay
+  float mom_coef;            // SGD momentum | Lion beta2
+  float update_coef;         // SGD 1 - dampening | Lion beta1
+  float one_minus_mom_coef;  // Lion only
+  float one_minus_update_coef;  // Lion only
+  float weight_decay;        // folded like FoAdamHyper.weight_decay
+  float decay;               // 1 - weight_decay when decoupled or Lion, else 1
   float grad_scale;
   int lion, nesterov, decoupled;
 } FoMomentumHyper;

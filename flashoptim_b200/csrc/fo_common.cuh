@@ -236,52 +236,80 @@ __device__ __forceinline__ uint4 round_to_shorts(const float2 (&s)[4]) {
 
 // ---------------------------------------------------------------- error correction (fast form)
 //
-// x = w + code / S * 2^ls with ls = E(w) - M - 1.  Both 2^ls / S and S * 2^-ls
-// are built by adding the exponent field of w (clamped from below, see Elem)
-// to the bit pattern of a constant, one integer instruction each.
+// x = w + code / S * 2^ls with ls = E(w) - M - 1 (S = 127 or 32767, M the
+// mantissa width of the narrow type, E its unbiased exponent).  2^E is the
+// narrow value with its mantissa masked off, one AND on the fp32 image, so
+//   decode:  x = w + (code * 2^-(M+1) / S) * 2^E
+//   encode:  code = round((x - w) * 2^-E * (S * 2^(M+1)))
+// For bf16 values below 2^-126 (zero and subnormals) the mask yields 0: their
+// correction, at most 2^-134, is dropped on decode and whatever the encoder
+// wrote for them is never used.  fp16 subnormals share the exponent of the
+// smallest normal, 2^-14, and are clamped there, which is exact.
 
-template <int kErrBytes>
+template <typename T, int kErrBytes>
 struct EccConst {
   static constexpr float kS = kErrBytes == 1 ? 127.0f : 32767.0f;
+  static constexpr float kHalfUlp = Elem<T>::kMant == 7 ? 0.00390625f : 0.00048828125f;  // 2^-(M+1)
+  static constexpr float kDec = kHalfUlp / kS;
+  static constexpr float kEnc = kS / kHalfUlp;
 };
 
-template <typename T, int kErrBytes>
-__device__ __forceinline__ float ecc_dec_scale(float w_as_f32) {
-  // bits(1/S) + (field - (128 + M)) << 23
-  const uint32_t inv_bits = kErrBytes == 1 ? 0x3C010204u /* 1/127 */ : 0x38000100u /* 1/32767 */;
+template <typename T>
+__device__ __forceinline__ uint32_t exp_field(float w_as_f32) {
   uint32_t f = __float_as_uint(w_as_f32) & 0x7F800000u;
-  f = max(f, Elem<T>::kMinExpField);
-  return __uint_as_float(f + (inv_bits - ((128u + Elem<T>::kMant) << 23)));
-}
-template <typename T, int kErrBytes>
-__device__ __forceinline__ float ecc_enc_scale(float w_as_f32) {
-  // bits(S) - (field - (128 + M)) << 23
-  const uint32_t s_bits = kErrBytes == 1 ? 0x42FE0000u /* 127 */ : 0x46FFFE00u /* 32767 */;
-  uint32_t f = __float_as_uint(w_as_f32) & 0x7F800000u;
-  f = max(f, Elem<T>::kMinExpField);
-  return __uint_as_float((s_bits + ((128u + Elem<T>::kMant) << 23)) - f);
+  if constexpr (Elem<T>::kMant == 10) f = max(f, 113u << 23);
+  return f;
 }
 
-// Master value from narrow value + codes (already widened to fp32).
+// 8 signed codes (int8: two words, int16: four words) scaled by kDec, as fp32.
 template <typename T, int kErrBytes>
-__device__ __forceinline__ void ecc_apply8(float2 (&w)[4], const float2 (&code)[4]) {
+__device__ __forceinline__ void ecc_codes_scaled(uint4 c, float2 (&q)[4]) {
+  constexpr float k = EccConst<T, kErrBytes>::kDec;
+  if constexpr (kErrBytes == 1) {
+    const uint32_t w[2] = {c.x ^ 0x80808080u, c.y ^ 0x80808080u};
+    // the offset 2^23 + 128 is subtracted exactly first: folding it into an FMA
+    // with k would round (2^23 + 128) * k and shift every code by up to a quarter step
+    const float2 kk = splat2(k), off = splat2(-(kMagic + 128.0f));
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 sc = make_float2(ecc_dec_scale<T, kErrBytes>(w[i].x), ecc_dec_scale<T, kErrBytes>(w[i].y));
-    w[i] = fma2(code[i], sc, w[i]);
+    for (int i = 0; i < 2; ++i) {
+      float2 a, b;
+      a.x = __uint_as_float(__byte_perm(w[i], kMagicBits, 0x7650));
+      a.y = __uint_as_float(__byte_perm(w[i], kMagicBits, 0x7651));
+      b.x = __uint_as_float(__byte_perm(w[i], kMagicBits, 0x7652));
+      b.y = __uint_as_float(__byte_perm(w[i], kMagicBits, 0x7653));
+      q[2 * i] = mul2(add2(a, off), kk);
+      q[2 * i + 1] = mul2(add2(b, off), kk);
+    }
+  } else {
+    float2 t[4];
+    s16_to_float(c, t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = mul2(t[i], splat2(k));
   }
 }
-// Scaled residual (in code units, not yet rounded) of x against its rounding.
+
+// Master value from narrow value (already widened) + scaled codes.
+template <typename T>
+__device__ __forceinline__ void ecc_apply8(float2 (&w)[4], const float2 (&code_scaled)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 e2 = make_float2(__uint_as_float(exp_field<T>(w[i].x)), __uint_as_float(exp_field<T>(w[i].y)));
+    w[i] = fma2(code_scaled[i], e2, w[i]);
+  }
+}
+// Residual of x against its rounding, in code units (not yet rounded to integer).
 template <typename T, int kErrBytes>
 __device__ __forceinline__ void ecc_residual8(const float2 (&x)[4], const float2 (&rounded)[4],
                                               float2 (&s)[4]) {
   const float2 neg1 = splat2(-1.0f);
+  const float2 kenc = splat2(EccConst<T, kErrBytes>::kEnc);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float2 e = fma2(rounded[i], neg1, x[i]);  // exact: |e| <= half an ULP of the rounding
-    float2 sc = make_float2(ecc_enc_scale<T, kErrBytes>(rounded[i].x),
-                            ecc_enc_scale<T, kErrBytes>(rounded[i].y));
-    s[i] = mul2(e, sc);
+    // 2^-E: exponent field 254 - field(w)
+    float2 r = make_float2(__uint_as_float(0x7F000000u - exp_field<T>(rounded[i].x)),
+                           __uint_as_float(0x7F000000u - exp_field<T>(rounded[i].y)));
+    s[i] = mul2(mul2(e, r), kenc);
   }
 }
 
@@ -298,21 +326,28 @@ __device__ __forceinline__ float group_max(float a) {
 __device__ __forceinline__ void dequant_softsign8(uint2 codes, float scale, float2 (&x)[4]) {
   float2 q[4];
   s8_to_float(codes, q);
+  const float2 sc = splat2(scale);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float2 r = make_float2(fast_rcp(254.0f - fabsf(q[i].x)), fast_rcp(254.0f - fabsf(q[i].y)));
-    x[i] = mul2(mul2(q[i], splat2(scale)), r);
+    x[i] = mul2(mul2(q[i], sc), r);
   }
 }
 // Unsigned sqrt-domain codes -> fp32: x = (scale * q / 255)^2.
 __device__ __forceinline__ void dequant_sqrt8(uint2 codes, float scale, float2 (&x)[4]) {
-  float2 q[4];
-  u8_to_float(codes, q);
-  const float2 sc = splat2(scale * (1.0f / 255.0f));
+  const uint32_t w[2] = {codes.x, codes.y};
+  const float k = scale * (1.0f / 255.0f);
+  const float2 kk = splat2(k), off = splat2(-kMagic * k);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 r = mul2(q[i], sc);
-    x[i] = mul2(r, r);
+  for (int i = 0; i < 2; ++i) {
+    float2 a, b;
+    a.x = __uint_as_float(__byte_perm(w[i], kMagicBits, 0x7650));
+    a.y = __uint_as_float(__byte_perm(w[i], kMagicBits, 0x7651));
+    b.x = __uint_as_float(__byte_perm(w[i], kMagicBits, 0x7652));
+    b.y = __uint_as_float(__byte_perm(w[i], kMagicBits, 0x7653));
+    float2 ra = fma2(a, kk, off), rb = fma2(b, kk, off);
+    x[2 * i] = mul2(ra, ra);
+    x[2 * i + 1] = mul2(rb, rb);
   }
 }
 
@@ -323,25 +358,23 @@ __device__ __forceinline__ float quant_softsign8(const float2 (&x)[4], uint2& co
   for (int i = 0; i < 4; ++i) a = fmaxf(a, fmaxf(fabsf(x[i].x), fabsf(x[i].y)));
   a = fmaxf(group_max(a), 1e-12f);
   float2 s[4];
-  const float2 k254 = splat2(254.0f);
+  const float inv254 = 1.0f / 254.0f;
+  const float a254 = a * inv254;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    // 127 * 2n / (1 + |n|) with n = x / a  ==  254 x / (a + |x|)
-    float2 r = make_float2(fast_rcp(a + fabsf(x[i].x)), fast_rcp(a + fabsf(x[i].y)));
-    s[i] = mul2(mul2(x[i], k254), r);
+    // 127 * 2n / (1 + |n|) with n = x / a  ==  x / ((a + |x|) / 254)
+    float2 r = make_float2(fast_rcp(fmaf(fabsf(x[i].x), inv254, a254)),
+                           fast_rcp(fmaf(fabsf(x[i].y), inv254, a254)));
+    s[i] = mul2(x[i], r);
   }
   codes = round_to_bytes(s);
   return a;
 }
-// fp32 (>= 0) -> unsigned sqrt-domain codes; returns the group's max sqrt (the scale).
-__device__ __forceinline__ float quant_sqrt8(const float2 (&x)[4], uint2& codes) {
-  float2 r[4];
+// sqrt-domain values (>= 0, already square-rooted) -> unsigned codes; returns the scale.
+__device__ __forceinline__ float quant_sqrt8_pre(const float2 (&r)[4], uint2& codes) {
   float a = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    r[i] = make_float2(fast_sqrt(x[i].x), fast_sqrt(x[i].y));
-    a = fmaxf(a, fmaxf(r[i].x, r[i].y));
-  }
+  for (int i = 0; i < 4; ++i) a = fmaxf(a, fmaxf(r[i].x, r[i].y));
   a = fmaxf(group_max(a), 1e-12f);
   const float2 k = splat2(255.0f * fast_rcp(a));
   float2 s[4];

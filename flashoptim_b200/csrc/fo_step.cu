@@ -14,10 +14,10 @@
 namespace fo {
 
 #ifndef FO_UNROLL
-#define FO_UNROLL 2
+#define FO_UNROLL 1
 #endif
 #ifndef FO_CTAS_PER_SM
-#define FO_CTAS_PER_SM 3
+#define FO_CTAS_PER_SM 4
 #endif
 #ifndef FO_THREADS
 #define FO_THREADS 256
@@ -40,16 +40,26 @@ struct StepParams {
   InlineTable inl;
 };
 
-template <typename T, int kErr, bool kQ>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm)
-    adam_kernel(const __grid_constant__ StepParams P, const __grid_constant__ FoAdamHyper H) {
-  const FoSeg* segs = P.segs ? P.segs : P.inl.segs;
-  const int32_t* cb = P.chunk_begin ? P.chunk_begin : P.inl.chunk_begin;
-  int seg = 0;
-  int seg_begin = cb[0], seg_end = cb[1];
-  FoSeg S = segs[0];
-  bool vec = seg_vector_safe(S);
-  for (int c = blockIdx.x; c < P.total_chunks; c += gridDim.x) {
+// Walks the chunk list of one CTA: chunk c belongs to the segment s with
+// chunk_begin[s] <= c < chunk_begin[s + 1]; a CTA visits chunks in increasing
+// order, so the segment index only ever moves forward.
+struct ChunkWalker {
+  const FoSeg* segs;
+  const int32_t* cb;
+  int total;
+  int seg, seg_begin, seg_end;
+  FoSeg S;
+  bool vec;
+
+  __device__ __forceinline__ ChunkWalker(const StepParams& P)
+      : segs(P.segs ? P.segs : P.inl.segs), cb(P.chunk_begin ? P.chunk_begin : P.inl.chunk_begin),
+        total(P.total_chunks), seg(0) {
+    seg_begin = cb[0];
+    seg_end = cb[1];
+    S = segs[0];
+    vec = seg_vector_safe(S);
+  }
+  __device__ __forceinline__ void seek(int c) {
     if (c >= seg_end) {
       do { ++seg; } while (c >= cb[seg + 1]);
       S = segs[seg];
@@ -57,24 +67,51 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       seg_end = cb[seg + 1];
       vec = seg_vector_safe(S);
     }
-    const int64_t chunk_base = (int64_t)(c - seg_begin) * kChunk;
-    UnitRegs<T, kErr, 2, kQ> r[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t base = chunk_base + (int64_t)(u * kThreads + threadIdx.x) * kUnit;
-      load_unit_state(r[u], S, base, vec);
-      load_unit_grad(r[u], S, base, vec);
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t base = chunk_base + (int64_t)(u * kThreads + threadIdx.x) * kUnit;
-      float2 p[4], g[4], m[4], v[4];
-      unpack8<T>(r[u].g, g);
-      widen_unit(r[u], p, m, v);
-      adam_update8(p, g, m, v, H);
-      store_unit(r[u], S, base, vec, p, m, v);
-    }
   }
+  __device__ __forceinline__ int64_t unit_base(int c, int u) const {
+    return (int64_t)(c - seg_begin) * kChunk + (int64_t)(u * kThreads + threadIdx.x) * kUnit;
+  }
+};
+
+// Occupancy (4 CTAs of 256 threads at 64 registers), not register-level software
+// prefetch, hides the memory latency here: a double-buffered variant of this loop
+// measured slower on B200 at every occupancy that its extra registers allowed.
+template <typename Regs, typename Load, typename Compute>
+__device__ __forceinline__ void walk_chunks(ChunkWalker& w, Load load, Compute compute) {
+  for (int c = blockIdx.x; c < w.total; c += gridDim.x) {
+    w.seek(c);
+    Regs r[kUnroll];
+    load(r, c);
+    compute(r, c);
+  }
+}
+
+template <typename T, int kErr, bool kQ>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+    adam_kernel(const __grid_constant__ StepParams P, const __grid_constant__ FoAdamHyper H) {
+  using Regs = UnitRegs<T, kErr, 2, kQ>;
+  ChunkWalker w(P);
+  walk_chunks<Regs>(
+      w,
+      [&](Regs(&r)[kUnroll], int c) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int64_t base = w.unit_base(c, u);
+          load_unit_state(r[u], w.S, base, w.vec);
+          load_unit_grad(r[u], w.S, base, w.vec);
+        }
+      },
+      [&](Regs(&r)[kUnroll], int c) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int64_t base = w.unit_base(c, u);
+          float2 p[4], g[4], m[4], v[4];
+          unpack8<T>(r[u].g, g);
+          widen_unit(r[u], p, m, v);
+          adam_update8<kQ>(p, g, m, v, H);
+          store_unit(r[u], w.S, base, w.vec, p, m, v);
+        }
+      });
 }
 
 template <typename T, int kErr, int kMode>
@@ -82,40 +119,31 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     momentum_kernel(const __grid_constant__ StepParams P, const __grid_constant__ FoMomentumHyper H) {
   constexpr int kStates = kMode == FO_STATE_NONE ? 0 : 1;
   constexpr bool kQ = kMode == FO_STATE_Q8;
-  const FoSeg* segs = P.segs ? P.segs : P.inl.segs;
-  const int32_t* cb = P.chunk_begin ? P.chunk_begin : P.inl.chunk_begin;
-  int seg = 0;
-  int seg_begin = cb[0], seg_end = cb[1];
-  FoSeg S = segs[0];
-  bool vec = seg_vector_safe(S);
-  for (int c = blockIdx.x; c < P.total_chunks; c += gridDim.x) {
-    if (c >= seg_end) {
-      do { ++seg; } while (c >= cb[seg + 1]);
-      S = segs[seg];
-      seg_begin = cb[seg];
-      seg_end = cb[seg + 1];
-      vec = seg_vector_safe(S);
-    }
-    const int64_t chunk_base = (int64_t)(c - seg_begin) * kChunk;
-    UnitRegs<T, kErr, kStates, kQ> r[kUnroll];
+  using Regs = UnitRegs<T, kErr, kStates, kQ>;
+  ChunkWalker w(P);
+  walk_chunks<Regs>(
+      w,
+      [&](Regs(&r)[kUnroll], int c) {
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t base = chunk_base + (int64_t)(u * kThreads + threadIdx.x) * kUnit;
-      load_unit_state(r[u], S, base, vec);
-      load_unit_grad(r[u], S, base, vec);
-    }
+        for (int u = 0; u < kUnroll; ++u) {
+          const int64_t base = w.unit_base(c, u);
+          load_unit_state(r[u], w.S, base, w.vec);
+          load_unit_grad(r[u], w.S, base, w.vec);
+        }
+      },
+      [&](Regs(&r)[kUnroll], int c) {
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t base = chunk_base + (int64_t)(u * kThreads + threadIdx.x) * kUnit;
-      float2 p[4], g[4], m[4], v[4];
+        for (int u = 0; u < kUnroll; ++u) {
+          const int64_t base = w.unit_base(c, u);
+          float2 p[4], g[4], m[4], v[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) m[i] = v[i] = make_float2(0.f, 0.f);
-      unpack8<T>(r[u].g, g);
-      widen_unit(r[u], p, m, v);
-      momentum_update8(p, g, m, H, kStates > 0);
-      store_unit(r[u], S, base, vec, p, m, v);
-    }
-  }
+          for (int i = 0; i < 4; ++i) m[i] = v[i] = make_float2(0.f, 0.f);
+          unpack8<T>(r[u].g, g);
+          widen_unit(r[u], p, m, v);
+          momentum_update8(p, g, m, H, kStates > 0);
+          store_unit(r[u], w.S, base, w.vec, p, m, v);
+        }
+      });
 }
 
 // ---------------------------------------------------------------- host side

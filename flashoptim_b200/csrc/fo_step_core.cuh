@@ -148,14 +148,10 @@ template <typename T, int kErr, int kStates, bool kQ>
 __device__ __forceinline__ void widen_unit(const UnitRegs<T, kErr, kStates, kQ>& r, float2 (&p)[4],
                                            float2 (&m)[4], float2 (&v)[4]) {
   unpack8<T>(r.p, p);
-  if constexpr (kErr == 1) {
+  if constexpr (kErr != 0) {
     float2 c[4];
-    s8_to_float(make_uint2(r.ecc.x, r.ecc.y), c);
-    ecc_apply8<T, 1>(p, c);
-  } else if constexpr (kErr == 2) {
-    float2 c[4];
-    s16_to_float(r.ecc, c);
-    ecc_apply8<T, 2>(p, c);
+    ecc_codes_scaled<T, kErr>(r.ecc, c);
+    ecc_apply8<T>(p, c);
   }
   if constexpr (kStates >= 1) {
     if constexpr (kQ) dequant_softsign8(r.q[0], r.sc[0], m);
@@ -172,6 +168,7 @@ template <typename T, int kErr, int kStates, bool kQ>
 __device__ __forceinline__ void store_unit(const UnitRegs<T, kErr, kStates, kQ>& r, const FoSeg& s,
                                            int64_t base, bool seg_vec, const float2 (&p)[4],
                                            const float2 (&m)[4], const float2 (&v)[4]) {
+  // when kQ, `v` holds the square root of the second state (what its codes store)
   const bool vec = seg_vec && r.cnt == kUnit;
   Raw8<T> pn;
   float2 back[4];
@@ -206,7 +203,7 @@ __device__ __forceinline__ void store_unit(const UnitRegs<T, kErr, kStates, kQ>&
     if constexpr (kQ) {
       uint2 codes;
       // every lane takes part in the group shuffle, valid unit or not
-      const float a = k == 0 ? quant_softsign8(x, codes) : quant_sqrt8(x, codes);
+      const float a = k == 0 ? quant_softsign8(x, codes) : quant_sqrt8_pre(x, codes);
       char* qp = static_cast<char*>(sp) + base;
       if (vec) st8(qp, codes);
       else if (r.cnt > 0) {
@@ -226,57 +223,75 @@ __device__ __forceinline__ void store_unit(const UnitRegs<T, kErr, kStates, kQ>&
 
 // ---------------------------------------------------------------- update rules on 8 elements
 
-__device__ __forceinline__ void adam_update8(float2 (&p)[4], float2 (&g)[4], float2 (&m)[4],
+// Adam / AdamW.  On return `v` holds the new second moment, or its square root
+// when kSqrtOut (the quantised state stores sqrt(v), and the denominator needs
+// the same square root: one evaluation serves both).
+template <bool kSqrtOut>
+__device__ __forceinline__ void adam_update8(float2 (&p)[4], const float2 (&g)[4], float2 (&m)[4],
                                              float2 (&v)[4], const FoAdamHyper& h) {
-  const float2 b1 = splat2(h.beta1), omb1 = splat2(1.0f - h.beta1);
-  const float2 b2 = splat2(h.beta2), omb2 = splat2(1.0f - h.beta2);
-  const float2 gs = splat2(h.grad_scale);
-  const float2 decay = splat2(h.decoupled ? 1.0f - h.weight_decay : 1.0f);
-  const float2 l2 = splat2(h.decoupled ? 0.0f : h.weight_decay);
+  const float2 b1 = splat2(h.beta1), b2 = splat2(h.beta2);
+  const float2 c1 = splat2(h.one_minus_beta1 * h.grad_scale);
   const float2 step = splat2(-h.lr * h.rbc1);
+  const float2 srbc2 = splat2(h.sqrt_rbc2), eps = splat2(h.eps);
+  if (h.decoupled) {
+    const float2 c2 = splat2(h.one_minus_beta2 * h.grad_scale * h.grad_scale);
+    const float2 decay = splat2(h.decay);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 gi = mul2(g[i], gs);
-    gi = fma2(p[i], l2, gi);
-    m[i] = fma2(m[i], b1, mul2(gi, omb1));
-    v[i] = fma2(v[i], b2, mul2(mul2(gi, gi), omb2));
-    float2 pd = mul2(p[i], decay);
-    float2 den;
-    den.x = fast_rcp(fast_sqrt(v[i].x * h.rbc2) + h.eps);
-    den.y = fast_rcp(fast_sqrt(v[i].y * h.rbc2) + h.eps);
-    p[i] = fma2(mul2(m[i], step), den, pd);
+    for (int i = 0; i < 4; ++i) {
+      m[i] = fma2(m[i], b1, mul2(g[i], c1));
+      float2 vn = fma2(v[i], b2, mul2(mul2(g[i], g[i]), c2));
+      float2 sv = make_float2(fast_sqrt(vn.x), fast_sqrt(vn.y));
+      float2 den = fma2(sv, srbc2, eps);
+      den = make_float2(fast_rcp(den.x), fast_rcp(den.y));
+      p[i] = fma2(mul2(m[i], step), den, mul2(p[i], decay));
+      v[i] = kSqrtOut ? sv : vn;
+    }
+  } else {
+    const float2 gs = splat2(h.grad_scale), l2 = splat2(h.weight_decay);
+    const float2 omb1 = splat2(h.one_minus_beta1), omb2 = splat2(h.one_minus_beta2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 gi = fma2(p[i], l2, mul2(g[i], gs));
+      m[i] = fma2(m[i], b1, mul2(gi, omb1));
+      float2 vn = fma2(v[i], b2, mul2(mul2(gi, gi), omb2));
+      float2 sv = make_float2(fast_sqrt(vn.x), fast_sqrt(vn.y));
+      float2 den = fma2(sv, srbc2, eps);
+      den = make_float2(fast_rcp(den.x), fast_rcp(den.y));
+      p[i] = fma2(mul2(m[i], step), den, p[i]);
+      v[i] = kSqrtOut ? sv : vn;
+    }
   }
 }
 
-__device__ __forceinline__ void momentum_update8(float2 (&p)[4], float2 (&g)[4], float2 (&m)[4],
+__device__ __forceinline__ void momentum_update8(float2 (&p)[4], const float2 (&g)[4], float2 (&m)[4],
                                                  const FoMomentumHyper& h, bool has_state) {
-  const float2 gs = splat2(h.grad_scale);
   const float2 mc = splat2(h.mom_coef);
   if (h.lion) {
-    const float2 uc = splat2(h.update_coef), omuc = splat2(1.0f - h.update_coef);
-    const float2 ommc = splat2(1.0f - h.mom_coef);
-    const float2 decay = splat2(1.0f - h.weight_decay);
+    const float2 uc = splat2(h.update_coef);
+    const float2 omuc = splat2(h.one_minus_update_coef * h.grad_scale);
+    const float2 ommc = splat2(h.one_minus_mom_coef * h.grad_scale);
+    const float2 decay = splat2(h.decay);
+    const uint32_t lr_bits = __float_as_uint(h.lr);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      float2 gi = mul2(g[i], gs);
-      float2 c = fma2(m[i], uc, mul2(gi, omuc));
-      m[i] = fma2(m[i], mc, mul2(gi, ommc));
-      float2 pd = mul2(p[i], decay);
+      float2 c = fma2(m[i], uc, mul2(g[i], omuc));
+      m[i] = fma2(m[i], mc, mul2(g[i], ommc));
+      // -lr * sign(c): lr with the flipped sign bit of c, or 0 when c == 0
       float2 u;
-      u.x = c.x > 0.0f ? -h.lr : (c.x < 0.0f ? h.lr : 0.0f);
-      u.y = c.y > 0.0f ? -h.lr : (c.y < 0.0f ? h.lr : 0.0f);
-      p[i] = add2(pd, u);
+      u.x = c.x == 0.0f ? 0.0f : __uint_as_float(lr_bits | (~__float_as_uint(c.x) & 0x80000000u));
+      u.y = c.y == 0.0f ? 0.0f : __uint_as_float(lr_bits | (~__float_as_uint(c.y) & 0x80000000u));
+      p[i] = fma2(p[i], decay, u);
     }
     return;
   }
-  const float2 decay = splat2(h.decoupled ? 1.0f - h.weight_decay : 1.0f);
+  const float2 decay = splat2(h.decay);
   const float2 l2 = splat2(h.decoupled ? 0.0f : h.weight_decay);
+  const float2 gs = splat2(h.grad_scale);
   const float2 ucoef = splat2(h.update_coef);
   const float2 nlr = splat2(-h.lr);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 gi = mul2(g[i], gs);
-    gi = fma2(p[i], l2, gi);
+    float2 gi = fma2(p[i], l2, mul2(g[i], gs));
     float2 pd = mul2(p[i], decay);
     if (!has_state) {
       p[i] = fma2(gi, nlr, pd);

@@ -42,9 +42,12 @@ class FoAdamHyper(Structure):
         ("beta1", c_float),
         ("beta2", c_float),
         ("eps", c_float),
+        ("one_minus_beta1", c_float),
+        ("one_minus_beta2", c_float),
         ("weight_decay", c_float),
+        ("decay", c_float),
         ("rbc1", c_float),
-        ("rbc2", c_float),
+        ("sqrt_rbc2", c_float),
         ("grad_scale", c_float),
         ("decoupled", c_int),
     ]
@@ -55,7 +58,10 @@ class FoMomentumHyper(Structure):
         ("lr", c_float),
         ("mom_coef", c_float),
         ("update_coef", c_float),
+        ("one_minus_mom_coef", c_float),
+        ("one_minus_update_coef", c_float),
         ("weight_decay", c_float),
+        ("decay", c_float),
         ("grad_scale", c_float),
         ("lion", c_int),
         ("nesterov", c_int),

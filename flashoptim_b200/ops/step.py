@@ -13,6 +13,7 @@ nothing is uploaded).  The reference launches one Triton kernel per tensor
 from __future__ import annotations
 
 import ctypes
+import math
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
@@ -22,6 +23,14 @@ import torch
 from . import native
 
 SEG_WORDS = 8  # int64 words per segment: p, g, ecc, s0, s0s, s1, s1s, n
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of fused step kernels launched by this process so far."""
+    return _launches
+
 
 
 @dataclass
@@ -39,9 +48,10 @@ class AdamHyper:
         from .oracle import bias_corrections
 
         rbc1, rbc2 = bias_corrections(self.beta1, self.beta2, self.step)
+        decay = 1.0 - self.weight_decay if self.decoupled else 1.0
         return native.FoAdamHyper(
-            self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, rbc1, rbc2,
-            self.grad_scale, int(self.decoupled),
+            self.lr, self.beta1, self.beta2, self.eps, 1.0 - self.beta1, 1.0 - self.beta2,
+            self.weight_decay, decay, rbc1, math.sqrt(rbc2), self.grad_scale, int(self.decoupled),
         )
 
 
@@ -57,9 +67,11 @@ class MomentumHyper:
     grad_scale: float = 1.0
 
     def to_c(self) -> native.FoMomentumHyper:
+        decay = 1.0 - self.weight_decay if (self.decoupled or self.lion) else 1.0
         return native.FoMomentumHyper(
-            self.lr, self.mom_coef, self.update_coef, self.weight_decay, self.grad_scale,
-            int(self.lion), int(self.nesterov), int(self.decoupled),
+            self.lr, self.mom_coef, self.update_coef, 1.0 - self.mom_coef, 1.0 - self.update_coef,
+            self.weight_decay, decay, self.grad_scale, int(self.lion), int(self.nesterov),
+            int(self.decoupled),
         )
 
 
@@ -130,6 +142,8 @@ def launch_adam(
             ctypes.byref(h), native.stream_ptr(table.device),
         )
     native.check(rc, "fo_adam_step")
+    global _launches
+    _launches += 1
 
 
 def launch_momentum(
@@ -152,6 +166,8 @@ def launch_momentum(
             ctypes.byref(h), native.stream_ptr(table.device),
         )
     native.check(rc, "fo_momentum_step")
+    global _launches
+    _launches += 1
 
 
 def make_rows(
