@@ -75,8 +75,10 @@ def _make_problem(n, dtype, err, quantized, states, seed, unaligned=False):
     if err:
         ecc = torch.zeros(n + off, dtype=torch.int8 if err == 1 else torch.int16, device="cuda")[off:]
         ecc.copy_(compute_ecc_bits(p32, p.contiguous(), master_bytewidth=2 + err))
-    m32 = _rand(n, torch.float32, 1e-3, seed + 2)
-    v32 = _rand(n, torch.float32, 1e-3, seed + 3).square()
+    # unquantised states live in the param dtype: keep v = O(1e-3) so that fp16 can hold it
+    sc = 3e-2 if (dtype == torch.float16 and not quantized) else 1e-3
+    m32 = _rand(n, torch.float32, sc, seed + 2)
+    v32 = _rand(n, torch.float32, sc, seed + 3).square()
     st = []
     for k in range(states):
         src = m32 if k == 0 else v32
