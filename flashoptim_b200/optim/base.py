@@ -20,8 +20,9 @@ What differs by design:
 * Without a GPU everything still works: CPU tensors take the PyTorch
   formulation of the same numerics (the reference raises
   ``NotImplementedError``, ``flashoptim/optimizers.py:484-493``).
-* Compressed checkpoints reload bit-exactly: codes and fp16 scales are shielded
-  from ``torch.optim.Optimizer.load_state_dict``'s cast to the parameter dtype.
+* Checkpoints reload without a detour through the parameter dtype: moments,
+  codes and fp16 scales are shielded from ``torch.optim.Optimizer.load_state_dict``'s
+  cast, so the compressed flavour round-trips bit-exactly.
 """
 
 from __future__ import annotations
@@ -131,9 +132,7 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         self._tables: dict[Any, SegmentTable] = {}
 
         defaults = dict(defaults or {})
-        defaults.update(
-            {"lr": lr, "initial_lr": lr, "master_bytewidth": master_bytewidth, "quantize": quantize}
-        )
+        defaults.update({"lr": lr, "master_bytewidth": master_bytewidth, "quantize": quantize})
         super().__init__(params, defaults=defaults)
 
         all_params = [p for g in self.param_groups for p in g["params"]]
@@ -155,6 +154,14 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
                 "for stable training.",
                 stacklevel=3,
             )
+
+    def add_param_group(self, param_group: dict[str, Any]) -> None:
+        # initial_lr is each group's own learning rate at creation (the reference
+        # stamps the constructor's lr on every group, flashoptim/optimizers.py:502-509,
+        # which skews decouple_lr for groups with their own lr)
+        super().add_param_group(param_group)
+        group = self.param_groups[-1]
+        group.setdefault("initial_lr", group["lr"])
 
     # ------------------------------------------------------------------ introspection
     def __repr__(self) -> str:
@@ -443,12 +450,19 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         PyTorch optimizer with the same state names (moments are re-quantised)."""
         sd = dict(state_dict)
         shielded_state = {}
+        moment_keys = set(self._quantized_state_spec())
+
+        def shield(k: str, v: Any) -> Any:
+            # moments (either flavour) keep their checkpoint dtype until they are
+            # re-quantised: a detour through an fp16 parameter dtype would flush
+            # small second moments to zero, through bf16 it would round the scales
+            if isinstance(v, torch.Tensor) and (k in moment_keys or k.split("::")[0] in moment_keys):
+                return _Shielded(v)
+            return v
+
         for idx, pstate in state_dict["state"].items():
             if isinstance(pstate, dict):
-                pstate = {
-                    k: (_Shielded(v) if isinstance(v, torch.Tensor) and "::" in k else v)
-                    for k, v in pstate.items()
-                }
+                pstate = {k: shield(k, v) for k, v in pstate.items()}
             shielded_state[idx] = pstate
         sd["state"] = shielded_state
         super().load_state_dict(sd)

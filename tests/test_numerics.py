@@ -1,0 +1,176 @@
+"""CPU tests of the numeric formats: group quantiser, master-weight split,
+state container, numerics-check arithmetic (modelled on the reference's
+``test/test_compression.py`` and ``test/test_ecc_invariants.py``)."""
+
+import math
+
+import pytest
+import torch
+
+from flashoptim_b200 import compute_ecc_bits, dequantize, quantize, reconstruct_fp32_param
+from flashoptim_b200.ops import oracle
+from flashoptim_b200.optim.state import MaybeQuantizedTensor, QuantizedTensorSpec
+
+from helpers import cossim
+
+SHAPES = [(1, 1), (17, 23), (1, 1000), (64, 64), (3, 5, 7), (4096,), (33,)]
+MODES = [(True, False, True), (True, False, False), (False, True, False), (False, True, True)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("signed,sqrt,softsign", MODES)
+def test_quantize_round_trip(shape, dtype, signed, sqrt, softsign):
+    for seed in range(4):
+        torch.manual_seed(seed)
+        x = (torch.randn(shape) * 10 ** (seed - 3)).to(dtype)
+        if not signed:
+            x = x.abs()
+        q, s = quantize(x, signed=signed, sqrt=sqrt, softsign=softsign)
+        assert q.shape == x.shape and q.dtype == (torch.int8 if signed else torch.uint8)
+        assert s.dtype == torch.float16 and s.numel() == math.ceil(x.numel() / 32)
+        y = dequantize(q, s, signed=signed, sqrt=sqrt, softsign=softsign)
+        assert y.dtype == torch.float32 and y.shape == x.shape
+        x32 = x.float()
+        if x.numel() >= 16:
+            assert cossim(x32, y) > 0.999
+        # error bound: half a code step of the (companded) grid, in the quantised domain
+        xd, yd = (x32.sqrt(), y.sqrt()) if sqrt else (x32, y)
+        groups = oracle.num_groups(x.numel())
+        pad = groups * 32 - x.numel()
+        xa = torch.nn.functional.pad(xd.flatten(), (0, pad)).view(groups, 32)
+        ya = torch.nn.functional.pad(yd.flatten(), (0, pad)).view(groups, 32)
+        absmax = xa.abs().amax(1, keepdim=True).clamp_min(1e-12)
+        qmax = 127.0 if signed else 255.0
+        # derivative of the inverse compander is at most 2 (at |n| = 1); fp16 scale adds 2^-11 relative
+        step = (2.0 if softsign else 1.0) * 0.5 / qmax
+        bound = absmax * (1.6 * step + 2 ** -10)
+        assert ((xa - ya).abs() <= bound + 1e-30).all()
+
+
+@pytest.mark.parametrize("n", [33, 63, 65, 1000, 1023, 1025, 4097])
+def test_quantize_tail_group(n):
+    """A partial last group is scaled by its own absmax and is no less accurate."""
+    torch.manual_seed(n)
+    x = torch.randn(n) * 1e-2
+    q, s = quantize(x)
+    y = dequantize(q, s)
+    tail = n - (n // 32) * 32
+    tail_absmax = x[-tail:].abs().max()
+    assert abs(float(s[-1]) - float(tail_absmax)) <= 3e-3 * float(tail_absmax)
+    err = (x - y).abs()
+    assert err[-tail:].max() <= 2 * err[:-tail].max() + 1e-12
+
+
+def test_quantize_zero_and_empty():
+    q, s = quantize(torch.zeros(70))
+    assert (q == 0).all() and (dequantize(q, s) == 0).all()
+    q, s = quantize(torch.zeros(0))
+    assert q.numel() == 0 and s.numel() == 0 and dequantize(q, s).numel() == 0
+
+
+def test_spec_validation():
+    QuantizedTensorSpec(signed=True, sqrt=False, softsign=True)
+    with pytest.raises(ValueError):
+        QuantizedTensorSpec(signed=1)  # type: ignore[arg-type]
+
+
+def test_maybe_quantized_tensor_states():
+    x = torch.randn(100) * 1e-3
+    t = MaybeQuantizedTensor(x, try_quantize=True)
+    assert t.is_quantized() and t.quantized.dtype == torch.int8 and t.scales.numel() == 4
+    assert t.shape == (100,) and t.numel() == 100 and not t.is_cuda
+    assert cossim(t.materialize(), x) > 0.999
+    sd = t.state_dict("exp_avg", allow_quantized=True)
+    assert set(sd) == {"exp_avg::quantized", "exp_avg::scales"}
+    sd_plain = t.state_dict("exp_avg", allow_quantized=False)
+    assert set(sd_plain) == {"exp_avg"} and sd_plain["exp_avg"].dtype == torch.bfloat16
+    u = MaybeQuantizedTensor(x, try_quantize=False, storage_dtype=torch.bfloat16)
+    assert not u.is_quantized() and u.data.dtype == torch.bfloat16
+    assert u.kernel_scales_or_self is u.data
+    # both checkpoint flavours load, mixing them is rejected
+    r = MaybeQuantizedTensor.from_state_dict(sd, "exp_avg")
+    assert torch.equal(r.quantized, t.quantized) and torch.equal(r.scales, t.scales)
+    r2 = MaybeQuantizedTensor.from_state_dict(sd_plain, "exp_avg")
+    assert r2.is_quantized()
+    with pytest.raises(ValueError):
+        MaybeQuantizedTensor.from_state_dict({**sd, **sd_plain}, "exp_avg")
+
+
+# ---------------------------------------------------------------- error correction
+
+
+def _all_mantissas_sample(dtype, exponent, sign, count=1 << 16):
+    """fp32 values with a fixed sign / exponent and evenly spread 23-bit mantissas."""
+    mant = torch.arange(0, 1 << 23, (1 << 23) // count, dtype=torch.int32)
+    bits = (sign << 31) | ((exponent + 127) << 23) | mant
+    return bits.to(torch.int32).view(torch.float32)
+
+
+@pytest.mark.parametrize("dtype,exponents", [
+    (torch.bfloat16, [-126, -100, -20, -1, 0, 1, 17, 100, 126]),
+    (torch.float16, [-14, -8, -1, 0, 3, 14]),
+])
+@pytest.mark.parametrize("sign", [0, 1])
+def test_ecc_invariants(dtype, exponents, sign):
+    for e in exponents:
+        x = _all_mantissas_sample(dtype, e, sign)
+        w = x.to(dtype)
+        finite = torch.isfinite(w.float())
+        x, w = x[finite], w[finite]
+        base_err = (w.float() - x).abs()
+        e8 = compute_ecc_bits(x, w, master_bytewidth=3)
+        e16 = compute_ecc_bits(x, w, master_bytewidth=4)
+        assert e8.dtype == torch.int8 and e16.dtype == torch.int16
+        r8 = reconstruct_fp32_param(w, e8)
+        r16 = reconstruct_fp32_param(w, e16)
+        err8, err16 = (r8 - x).abs(), (r16 - x).abs()
+        ulp32 = torch.exp2(torch.floor(torch.log2(x.abs())) - 23)
+        # 1. the correction never hurts (beyond one fp32 rounding)
+        assert (err8 <= base_err + ulp32).all()
+        # 2. wider codes are at least as good
+        assert (err16 <= err8 + ulp32).all()
+        # 3. residual is bounded by half a code step of half an ULP
+        half_ulp = torch.exp2(oracle.ecc_log_scale(w).float())
+        assert (err8 <= half_ulp * 0.5 / 127 * 1.01 + ulp32).all()
+        assert (err16 <= half_ulp * 0.5 / 32767 * 1.01 + ulp32).all()
+        # 4. exactly representable values need no correction
+        exact = w.float() == x
+        assert (e8[exact] == 0).all() and (e16[exact] == 0).all()
+        # 5. codes stay inside the symmetric range
+        assert e8.abs().max() <= 127 and e16.abs().max() <= 32767
+
+
+def test_ecc_zero_and_subnormal_inputs():
+    x = torch.tensor([0.0, -0.0, 1e-40, -1e-39, 6e-8, 1e-45])
+    for dtype in (torch.bfloat16, torch.float16):
+        w = x.to(dtype)
+        for mbw in (3, 4):
+            e = compute_ecc_bits(x, w, master_bytewidth=mbw)
+            r = reconstruct_fp32_param(w, e)
+            assert torch.isfinite(r).all()
+            assert ((r - x).abs() <= (w.float() - x).abs() + 1e-45).all()
+
+
+def test_ecc_api_validation():
+    w = torch.zeros(4, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        reconstruct_fp32_param(torch.zeros(4), torch.zeros(4, dtype=torch.int8))
+    with pytest.raises(ValueError):
+        reconstruct_fp32_param(w, torch.zeros(4, dtype=torch.int32))
+    with pytest.raises(ValueError):
+        compute_ecc_bits(torch.zeros(4, dtype=torch.bfloat16), w)
+    with pytest.raises(ValueError):
+        compute_ecc_bits(torch.zeros(4), torch.zeros(4))
+    with pytest.raises(ValueError):
+        compute_ecc_bits(torch.zeros(4), w, master_bytewidth=6)
+
+
+def test_min_expressible_step():
+    # bf16, no ECC: 7 mantissa bits; a weight of 1.0 needs steps > 0.49 * 2^-7
+    v = oracle.log2_min_expressible_step(torch.bfloat16, 1.0, 0)
+    assert abs(v - (-(16 - 1 - 8) - math.log2(0.49))) < 1e-9
+    # 24-bit masters add 8 mantissa bits, 32-bit masters 16
+    assert oracle.log2_min_expressible_step(torch.bfloat16, 1.0, 3) == pytest.approx(v - 8)
+    assert oracle.log2_min_expressible_step(torch.bfloat16, 1.0, 4) == pytest.approx(v - 16)
+    assert oracle.log2_min_expressible_step(torch.bfloat16, 4.5, 0) == pytest.approx(v + 2)
