@@ -97,6 +97,61 @@ int fo_ecc_encode(const float* x, const void* narrow, int dtype, void* ecc, int 
 // max |x| of a tensor, accumulated into *out (a float the caller zeroed).
 int fo_maxabs(const void* x, int dtype, int64_t n, float* out, void* stream);
 
+// ---------------------------------------------------------------------------
+// Steps fused with the gradient collective over NVLink peer memory (fo_comm.cu)
+// ---------------------------------------------------------------------------
+
+enum { FO_MAX_PEERS = 8 };
+
+// One rank's view of a group of `world` GPUs on one node.
+//   grad[r]      rank r's gradient buffer (symmetric: same layout on every rank),
+//                as mapped into this process; FoSeg.g is a BYTE OFFSET into it
+//   multicast    NVSwitch multicast mapping of the same buffer, or null: when set,
+//                full aligned units are fetched with multimem.ld_reduce
+//   pad[r]       rank r's signal pad: uint32 words [channel * FO_MAX_PEERS + src]
+//   status       3 local uint32 words, zeroed by the host before first use:
+//                [0] bit mask of channels whose wait timed out, [1] 1 + rank that
+//                was missing, [2] CTA counter (internal)
+//   epoch        value published / awaited on the channels; grows by one per use
+//   ready_channel  flag "my buffer holds this epoch's gradients"
+//   done_channel   flag "I have finished reading everybody's buffer for this epoch"
+//   grad_out     optional: the averaged gradient is also written to
+//                grad_out + (FoSeg.g + unit offset - grad_out_sub)
+//   timeout_ns   limit of every device-side wait
+typedef struct FoCommArgs {
+  const void* grad[FO_MAX_PEERS];
+  const void* multicast;
+  uint32_t* pad[FO_MAX_PEERS];
+  uint32_t* status;
+  void* grad_out;
+  int64_t grad_out_sub;
+  uint64_t timeout_ns;
+  uint32_t epoch;
+  int world, rank;
+  int ready_channel, done_channel;
+} FoCommArgs;
+
+// Elements per CTA iteration of the peer kernels (for the chunk prefix).
+int fo_comm_chunk_elems(void);
+
+// `segs` and `chunk_begin` are DEVICE pointers.  The gradient of every element
+// is hyper->grad_scale times the sum over ranks (pass 1 / world for a mean).
+int fo_adam_step_peer(const FoSeg* segs, const int32_t* chunk_begin, int n_seg, int total_chunks, int dtype,
+                      int err_bytes, int quantized, const FoAdamHyper* hyper, const FoCommArgs* comm,
+                      void* stream);
+int fo_momentum_step_peer(const FoSeg* segs, const int32_t* chunk_begin, int n_seg, int total_chunks,
+                          int dtype, int err_bytes, int state_mode, const FoMomentumHyper* hyper,
+                          const FoCommArgs* comm, void* stream);
+// out[i] = scale * sum_r grad[r][src_offset_bytes + i] for n elements (no update).
+int fo_reduce_peer(int64_t n, int64_t src_offset_bytes, void* out, int dtype, float scale,
+                   const FoCommArgs* comm, void* stream);
+// All-gather inside the symmetric buffer: every rank pulls slot s (slot_bytes
+// each, a multiple of 16) from rank s into its own copy.
+int fo_allgather_peer(int64_t slot_bytes, const FoCommArgs* comm, void* stream);
+// Publish / await comm->epoch on one channel from a one-CTA kernel.
+int fo_comm_signal(const FoCommArgs* comm, int channel, void* stream);
+int fo_comm_wait(const FoCommArgs* comm, int channel, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

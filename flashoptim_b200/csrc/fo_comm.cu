@@ -1,0 +1,473 @@
+// Optimizer steps fused with the gradient collective over NVLink peer memory.
+//
+// The gradient of every element is the average of the copies that the W ranks
+// hold in a symmetric buffer (same layout at the same offset on every GPU,
+// each mapped into every process).  One kernel per rank reads the W copies
+// straight into registers -- plain peer loads in a fixed rank order, or one
+// multimem.ld_reduce through the NVSwitch when a multicast mapping exists --
+// and runs the same per-unit update as the local step kernels, so the reduced
+// gradient never exists in HBM and no collective library is involved:
+//   * DDP bucket: every rank reduces the whole bucket and updates its replica
+//     (one-shot all-reduce fused with the update; rank order is fixed, so all
+//     replicas compute bit-identical sums);
+//   * FSDP2: rank r reduces only row r of the [W, shard] reduce-scatter input
+//     and updates its shard (reduce-scatter fused with the sharded update).
+// The reference leaves both collectives to NCCL inside PyTorch's DDP / FSDP2
+// and then launches its update per tensor (flashoptim/optimizers.py:597-616).
+//
+// Cross-GPU ordering uses epoch flags in a symmetric "signal pad": word
+// [channel * FO_MAX_PEERS + src] of rank d's pad is written only by rank src.
+// Every wait is bounded by a wall-clock limit (globaltimer); a wait that runs
+// out records a code in a local status word, the kernel skips its work and
+// returns normally, and the host raises.  No TMA or multicast-cluster loads
+// are used anywhere in this file.
+#include "fo_step_core.cuh"
+
+namespace fo {
+
+constexpr int kCommThreads = 256;
+constexpr int kCommChunk = kCommThreads * kUnit;
+constexpr int kCommCtasPerSm = 3;
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Epochs only grow; a flag satisfies a wait once it has reached the epoch
+// (signed difference, so wrap-around after 2^31 steps is harmless).
+__device__ __forceinline__ bool epoch_reached(uint32_t flag, uint32_t epoch) {
+  return (int32_t)(flag - epoch) >= 0;
+}
+
+// Thread `t < world` waits until rank t's flag on `channel` reaches `epoch`.
+// Returns false on timeout (and records it).
+__device__ __forceinline__ bool wait_flag(const FoCommArgs& A, int channel, int src, uint32_t epoch) {
+  const uint32_t* flag = A.pad[A.rank] + channel * FO_MAX_PEERS + src;
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    if (epoch_reached(ld_acquire_sys(flag), epoch)) return true;
+    if (global_ns() - t0 > A.timeout_ns) {
+      atomicOr(reinterpret_cast<unsigned int*>(A.status), 1u << (channel & 31));
+      atomicExch(reinterpret_cast<unsigned int*>(A.status) + 1, (unsigned int)src + 1u);
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
+
+// Every CTA: wait until all ranks have published `epoch` on the ready channel.
+// CTA 0 also publishes this rank's own arrival first.  Returns false (for the
+// whole CTA) if any wait ran out.
+__device__ __forceinline__ bool start_barrier(const FoCommArgs& A) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < A.world) {
+    __threadfence_system();
+    st_release_sys(A.pad[threadIdx.x] + A.ready_channel * FO_MAX_PEERS + A.rank, A.epoch);
+  }
+  if (threadIdx.x < A.world) {
+    if (!wait_flag(A, A.ready_channel, threadIdx.x, A.epoch)) ok = 0;
+  }
+  __syncthreads();
+  return ok != 0;
+}
+
+// After the main loop: the last CTA to finish tells every peer that this rank
+// no longer reads their buffers for `epoch` (done channel).
+__device__ __forceinline__ void end_signal(const FoCommArgs& A) {
+  __shared__ int last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    unsigned int n = atomicAdd(reinterpret_cast<unsigned int*>(A.status) + 2, 1u);
+    last = (n == gridDim.x - 1);
+    if (last) reinterpret_cast<unsigned int*>(A.status)[2] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (last && threadIdx.x < A.world) {
+    __threadfence_system();
+    st_release_sys(A.pad[threadIdx.x] + A.done_channel * FO_MAX_PEERS + A.rank, A.epoch);
+  }
+}
+
+// ---------------------------------------------------------------- gradient from peers
+
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_f16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_f32x4(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+
+// Sum of the W copies of one unit, in fp32, in rank order.  `off` is the byte
+// offset of the unit inside every rank's buffer.
+template <typename T>
+__device__ __forceinline__ void reduce_unit(const FoCommArgs& A, int64_t off, int cnt, bool vec,
+                                            float2 (&g)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) g[i] = make_float2(0.f, 0.f);
+  if (cnt <= 0) return;
+  if (vec && A.multicast != nullptr) {
+    Raw8<T> r;
+    const char* a = static_cast<const char*>(A.multicast) + off;
+    if constexpr (sizeof(T) == 4) {
+      r.v = multimem_ld_reduce_f32x4(a);
+      r.w = multimem_ld_reduce_f32x4(a + 16);
+    } else if constexpr (Elem<T>::kMant == 7) {
+      r.v = multimem_ld_reduce_bf16x8(a);
+    } else {
+      r.v = multimem_ld_reduce_f16x8(a);
+    }
+    unpack8<T>(r, g);
+    return;
+  }
+  // all loads first, then the adds: W independent requests in flight per thread
+  Raw8<T> r[FO_MAX_PEERS];
+#pragma unroll
+  for (int p = 0; p < FO_MAX_PEERS; ++p) {
+    if (p < A.world) {
+      const T* src = reinterpret_cast<const T*>(static_cast<const char*>(A.grad[p]) + off);
+      r[p].v = make_uint4(0, 0, 0, 0);
+      if constexpr (sizeof(T) == 4) r[p].w = make_uint4(0, 0, 0, 0);
+      if (vec) load_raw8<T>(r[p], src, true);
+      else load_raw8_partial<T>(r[p], src, cnt);
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < FO_MAX_PEERS; ++p) {
+    if (p < A.world) {
+      float2 x[4];
+      unpack8<T>(r[p], x);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) g[i] = add2(g[i], x[i]);
+    }
+  }
+}
+
+struct CommWalker {
+  const FoSeg* segs;
+  const int32_t* cb;
+  int seg, seg_begin, seg_end;
+  FoSeg S;
+  bool vec;
+  __device__ __forceinline__ CommWalker(const FoSeg* s, const int32_t* c) : segs(s), cb(c), seg(0) {
+    seg_begin = cb[0];
+    seg_end = cb[1];
+    S = segs[0];
+    vec = vector_safe();
+  }
+  // S.g holds a byte offset into the symmetric buffers here, not a pointer
+  __device__ __forceinline__ bool vector_safe() const {
+    uintptr_t a = reinterpret_cast<uintptr_t>(S.p) | reinterpret_cast<uintptr_t>(S.g) |
+                  reinterpret_cast<uintptr_t>(S.ecc) | reinterpret_cast<uintptr_t>(S.s0) |
+                  reinterpret_cast<uintptr_t>(S.s1);
+    return (a & 15) == 0;
+  }
+  __device__ __forceinline__ void seek(int c) {
+    if (c >= seg_end) {
+      do { ++seg; } while (c >= cb[seg + 1]);
+      S = segs[seg];
+      seg_begin = cb[seg];
+      seg_end = cb[seg + 1];
+      vec = vector_safe();
+    }
+  }
+};
+
+// Writes the averaged gradient of one unit to `grad_out` (optional).
+template <typename T>
+__device__ __forceinline__ void store_grad_out(const FoCommArgs& A, int64_t goff, int cnt, bool vec,
+                                               const float2 (&g)[4], float scale) {
+  if (A.grad_out == nullptr || cnt <= 0) return;
+  float2 s[4], back[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s[i] = mul2(g[i], splat2(scale));
+  Raw8<T> r;
+  pack8<T>(s, r, back);
+  T* dst = reinterpret_cast<T*>(static_cast<char*>(A.grad_out) + (goff - A.grad_out_sub));
+  const bool v = vec && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+  store_raw8<T>(r, dst, cnt, v);
+}
+
+template <typename T, int kErr, bool kQ>
+__global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
+    adam_peer_kernel(const FoSeg* __restrict__ segs, const int32_t* __restrict__ cb, int total_chunks,
+                     const __grid_constant__ FoAdamHyper H, const __grid_constant__ FoCommArgs A) {
+  if (!start_barrier(A)) return;
+  using Regs = UnitRegs<T, kErr, 2, kQ>;
+  CommWalker w(segs, cb);
+  for (int c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+    w.seek(c);
+    const int64_t base = (int64_t)(c - w.seg_begin) * kCommChunk + (int64_t)threadIdx.x * kUnit;
+    Regs r;
+    load_unit_state(r, w.S, base, w.vec);
+    const bool vec = w.vec && r.cnt == kUnit;
+    const int64_t goff = (int64_t)reinterpret_cast<intptr_t>(w.S.g) + base * (int64_t)sizeof(T);
+    float2 p[4], g[4], m[4], v[4];
+    reduce_unit<T>(A, goff, r.cnt, vec, g);
+    store_grad_out<T>(A, goff, r.cnt, vec, g, H.grad_scale);
+    widen_unit(r, p, m, v);
+    adam_update8<kQ>(p, g, m, v, H);
+    store_unit(r, w.S, base, w.vec, p, m, v);
+  }
+  end_signal(A);
+}
+
+template <typename T, int kErr, int kMode>
+__global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
+    momentum_peer_kernel(const FoSeg* __restrict__ segs, const int32_t* __restrict__ cb, int total_chunks,
+                         const __grid_constant__ FoMomentumHyper H, const __grid_constant__ FoCommArgs A) {
+  if (!start_barrier(A)) return;
+  constexpr int kStates = kMode == FO_STATE_NONE ? 0 : 1;
+  constexpr bool kQ = kMode == FO_STATE_Q8;
+  using Regs = UnitRegs<T, kErr, kStates, kQ>;
+  CommWalker w(segs, cb);
+  for (int c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+    w.seek(c);
+    const int64_t base = (int64_t)(c - w.seg_begin) * kCommChunk + (int64_t)threadIdx.x * kUnit;
+    Regs r;
+    load_unit_state(r, w.S, base, w.vec);
+    const bool vec = w.vec && r.cnt == kUnit;
+    const int64_t goff = (int64_t)reinterpret_cast<intptr_t>(w.S.g) + base * (int64_t)sizeof(T);
+    float2 p[4], g[4], m[4], v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m[i] = v[i] = make_float2(0.f, 0.f);
+    reduce_unit<T>(A, goff, r.cnt, vec, g);
+    store_grad_out<T>(A, goff, r.cnt, vec, g, H.grad_scale);
+    widen_unit(r, p, m, v);
+    momentum_update8(p, g, m, H, kStates > 0);
+    store_unit(r, w.S, base, w.vec, p, m, v);
+  }
+  end_signal(A);
+}
+
+// Plain averaged reduce (no update): out[i] = scale * sum_r peer_r[off + i].
+// DDP buckets that must hand reduced gradients back, and the baseline for the
+// fused kernels' comparisons.
+template <typename T>
+__global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
+    reduce_peer_kernel(int64_t n, int64_t src_off, T* __restrict__ out, float scale,
+                       const __grid_constant__ FoCommArgs A) {
+  if (!start_barrier(A)) return;
+  const int64_t n_units = (n + kUnit - 1) / kUnit;
+  const bool aligned = ((src_off | reinterpret_cast<intptr_t>(out)) & 15) == 0;
+  for (int64_t u = (int64_t)blockIdx.x * kCommThreads + threadIdx.x; u < n_units;
+       u += (int64_t)gridDim.x * kCommThreads) {
+    const int64_t base = u * kUnit;
+    const int64_t left = n - base;
+    const int cnt = left >= kUnit ? kUnit : (int)left;
+    const bool vec = aligned && cnt == kUnit;
+    float2 g[4], s[4], back[4];
+    reduce_unit<T>(A, src_off + base * (int64_t)sizeof(T), cnt, vec, g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] = mul2(g[i], splat2(scale));
+    Raw8<T> r;
+    pack8<T>(s, r, back);
+    store_raw8<T>(r, out + base, cnt, vec);
+  }
+  end_signal(A);
+}
+
+// All-gather by pulling: rank r copies slot s of rank s's buffer (at s * slot_bytes)
+// into slot s of its own buffer, for every s != r.  Buffers are symmetric.
+__global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
+    allgather_pull_kernel(int64_t slot_bytes, const __grid_constant__ FoCommArgs A) {
+  if (!start_barrier(A)) return;
+  const int64_t n16 = slot_bytes / 16;  // slots are multiples of 16 bytes (checked by the host)
+  for (int s = 0; s < A.world; ++s) {
+    if (s == A.rank) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(A.grad[s]) + s * slot_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(const_cast<void*>(A.grad[A.rank])) + s * slot_bytes);
+    for (int64_t i = (int64_t)blockIdx.x * kCommThreads + threadIdx.x; i < n16;
+         i += (int64_t)gridDim.x * kCommThreads)
+      dst[i] = src[i];
+  }
+  end_signal(A);
+}
+
+// Stand-alone flag operations (one CTA).
+__global__ void signal_kernel(const __grid_constant__ FoCommArgs A, int channel) {
+  if (threadIdx.x < A.world) {
+    __threadfence_system();
+    st_release_sys(A.pad[threadIdx.x] + channel * FO_MAX_PEERS + A.rank, A.epoch);
+  }
+}
+__global__ void wait_kernel(const __grid_constant__ FoCommArgs A, int channel) {
+  if (threadIdx.x < A.world) wait_flag(A, channel, threadIdx.x, A.epoch);
+}
+
+static int comm_grid(int64_t work_ctas) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  int64_t g = (int64_t)sms * kCommCtasPerSm;
+  if (work_ctas < g) g = work_ctas;
+  return g < 1 ? 1 : (int)g;
+}
+
+static bool args_ok(const FoCommArgs* a) {
+  return a && a->world >= 1 && a->world <= FO_MAX_PEERS && a->rank >= 0 && a->rank < a->world && a->status;
+}
+
+template <typename T, int kErr>
+static int launch_adam_peer_q(const FoSeg* s, const int32_t* cb, int total, const FoAdamHyper& H,
+                              const FoCommArgs& A, int quantized, int grid, cudaStream_t st) {
+  if (quantized) adam_peer_kernel<T, kErr, true><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+  else adam_peer_kernel<T, kErr, false><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+  return (int)cudaGetLastError();
+}
+template <typename T>
+static int launch_adam_peer(const FoSeg* s, const int32_t* cb, int total, const FoAdamHyper& H,
+                            const FoCommArgs& A, int err, int quantized, int grid, cudaStream_t st) {
+  if constexpr (Elem<T>::kNarrow) {
+    if (err == 1) return launch_adam_peer_q<T, 1>(s, cb, total, H, A, quantized, grid, st);
+    if (err == 2) return launch_adam_peer_q<T, 2>(s, cb, total, H, A, quantized, grid, st);
+  }
+  if (err != 0) return (int)cudaErrorInvalidValue;
+  return launch_adam_peer_q<T, 0>(s, cb, total, H, A, quantized, grid, st);
+}
+
+template <typename T, int kErr>
+static int launch_mom_peer_m(const FoSeg* s, const int32_t* cb, int total, const FoMomentumHyper& H,
+                             const FoCommArgs& A, int mode, int grid, cudaStream_t st) {
+  switch (mode) {
+    case FO_STATE_NONE:
+      momentum_peer_kernel<T, kErr, FO_STATE_NONE><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+      break;
+    case FO_STATE_Q8:
+      momentum_peer_kernel<T, kErr, FO_STATE_Q8><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+      break;
+    case FO_STATE_FULL:
+      momentum_peer_kernel<T, kErr, FO_STATE_FULL><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+      break;
+    default: return (int)cudaErrorInvalidValue;
+  }
+  return (int)cudaGetLastError();
+}
+template <typename T>
+static int launch_mom_peer(const FoSeg* s, const int32_t* cb, int total, const FoMomentumHyper& H,
+                           const FoCommArgs& A, int err, int mode, int grid, cudaStream_t st) {
+  if constexpr (Elem<T>::kNarrow) {
+    if (err == 1) return launch_mom_peer_m<T, 1>(s, cb, total, H, A, mode, grid, st);
+    if (err == 2) return launch_mom_peer_m<T, 2>(s, cb, total, H, A, mode, grid, st);
+  }
+  if (err != 0) return (int)cudaErrorInvalidValue;
+  return launch_mom_peer_m<T, 0>(s, cb, total, H, A, mode, grid, st);
+}
+
+}  // namespace fo
+
+extern "C" int fo_comm_chunk_elems(void) { return fo::kCommChunk; }
+
+extern "C" int fo_adam_step_peer(const FoSeg* segs, const int32_t* chunk_begin, int n_seg, int total_chunks,
+                                 int dtype, int err_bytes, int quantized, const FoAdamHyper* hyper,
+                                 const FoCommArgs* comm, void* stream) {
+  if (!fo::args_ok(comm) || !hyper) return (int)cudaErrorInvalidValue;
+  if (n_seg <= 0 || total_chunks <= 0) return 0;
+  const int grid = fo::comm_grid(total_chunks);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case FO_BF16:
+      return fo::launch_adam_peer<__nv_bfloat16>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes,
+                                                 quantized, grid, st);
+    case FO_FP16:
+      return fo::launch_adam_peer<__half>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, quantized,
+                                          grid, st);
+    case FO_FP32:
+      return fo::launch_adam_peer<float>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, quantized,
+                                         grid, st);
+  }
+  return (int)cudaErrorInvalidValue;
+}
+
+extern "C" int fo_momentum_step_peer(const FoSeg* segs, const int32_t* chunk_begin, int n_seg,
+                                     int total_chunks, int dtype, int err_bytes, int state_mode,
+                                     const FoMomentumHyper* hyper, const FoCommArgs* comm, void* stream) {
+  if (!fo::args_ok(comm) || !hyper) return (int)cudaErrorInvalidValue;
+  if (n_seg <= 0 || total_chunks <= 0) return 0;
+  const int grid = fo::comm_grid(total_chunks);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case FO_BF16:
+      return fo::launch_mom_peer<__nv_bfloat16>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes,
+                                                state_mode, grid, st);
+    case FO_FP16:
+      return fo::launch_mom_peer<__half>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, state_mode,
+                                         grid, st);
+    case FO_FP32:
+      return fo::launch_mom_peer<float>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, state_mode,
+                                        grid, st);
+  }
+  return (int)cudaErrorInvalidValue;
+}
+
+extern "C" int fo_reduce_peer(int64_t n, int64_t src_offset_bytes, void* out, int dtype, float scale,
+                              const FoCommArgs* comm, void* stream) {
+  if (!fo::args_ok(comm)) return (int)cudaErrorInvalidValue;
+  if (n <= 0) return 0;
+  const int grid = fo::comm_grid((n + fo::kCommChunk - 1) / fo::kCommChunk);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case FO_BF16:
+      fo::reduce_peer_kernel<<<grid, fo::kCommThreads, 0, st>>>(n, src_offset_bytes, (__nv_bfloat16*)out, scale,
+                                                                *comm);
+      break;
+    case FO_FP16:
+      fo::reduce_peer_kernel<<<grid, fo::kCommThreads, 0, st>>>(n, src_offset_bytes, (__half*)out, scale, *comm);
+      break;
+    case FO_FP32:
+      fo::reduce_peer_kernel<<<grid, fo::kCommThreads, 0, st>>>(n, src_offset_bytes, (float*)out, scale, *comm);
+      break;
+    default: return (int)cudaErrorInvalidValue;
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fo_allgather_peer(int64_t slot_bytes, const FoCommArgs* comm, void* stream) {
+  if (!fo::args_ok(comm) || slot_bytes < 0 || (slot_bytes & 15)) return (int)cudaErrorInvalidValue;
+  if (slot_bytes == 0) return 0;
+  const int grid = fo::comm_grid((slot_bytes / 16 + fo::kCommThreads - 1) / fo::kCommThreads);
+  fo::allgather_pull_kernel<<<grid, fo::kCommThreads, 0, static_cast<cudaStream_t>(stream)>>>(slot_bytes, *comm);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fo_comm_signal(const FoCommArgs* comm, int channel, void* stream) {
+  if (!fo::args_ok(comm)) return (int)cudaErrorInvalidValue;
+  fo::signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(*comm, channel);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fo_comm_wait(const FoCommArgs* comm, int channel, void* stream) {
+  if (!fo::args_ok(comm)) return (int)cudaErrorInvalidValue;
+  fo::wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(*comm, channel);
+  return (int)cudaGetLastError();
+}

@@ -69,6 +69,26 @@ class FoMomentumHyper(Structure):
     ]
 
 
+FO_MAX_PEERS = 8
+
+
+class FoCommArgs(Structure):
+    _fields_ = [
+        ("grad", c_void_p * FO_MAX_PEERS),
+        ("multicast", c_void_p),
+        ("pad", c_void_p * FO_MAX_PEERS),
+        ("status", c_void_p),
+        ("grad_out", c_void_p),
+        ("grad_out_sub", c_int64),
+        ("timeout_ns", ctypes.c_uint64),
+        ("epoch", ctypes.c_uint32),
+        ("world", c_int),
+        ("rank", c_int),
+        ("ready_channel", c_int),
+        ("done_channel", c_int),
+    ]
+
+
 class NativeError(RuntimeError):
     """A kernel launch of libflashoptim_b200.so returned a CUDA error code."""
 
@@ -100,6 +120,26 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.fo_ecc_encode.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p]
     lib.fo_maxabs.restype = c_int
     lib.fo_maxabs.argtypes = [c_void_p, c_int, c_int64, c_void_p, c_void_p]
+    lib.fo_comm_chunk_elems.restype = c_int
+    lib.fo_comm_chunk_elems.argtypes = []
+    lib.fo_adam_step_peer.restype = c_int
+    lib.fo_adam_step_peer.argtypes = [
+        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, POINTER(FoAdamHyper), POINTER(FoCommArgs),
+        c_void_p,
+    ]
+    lib.fo_momentum_step_peer.restype = c_int
+    lib.fo_momentum_step_peer.argtypes = [
+        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, POINTER(FoMomentumHyper),
+        POINTER(FoCommArgs), c_void_p,
+    ]
+    lib.fo_reduce_peer.restype = c_int
+    lib.fo_reduce_peer.argtypes = [c_int64, c_int64, c_void_p, c_int, c_float, POINTER(FoCommArgs), c_void_p]
+    lib.fo_allgather_peer.restype = c_int
+    lib.fo_allgather_peer.argtypes = [c_int64, POINTER(FoCommArgs), c_void_p]
+    lib.fo_comm_signal.restype = c_int
+    lib.fo_comm_signal.argtypes = [POINTER(FoCommArgs), c_int, c_void_p]
+    lib.fo_comm_wait.restype = c_int
+    lib.fo_comm_wait.argtypes = [POINTER(FoCommArgs), c_int, c_void_p]
 
 
 def load(path: Optional[str] = None) -> ctypes.CDLL:

@@ -93,10 +93,17 @@ class SegmentTable:
             raise ValueError("too many elements for one multi-tensor launch")
         return cb.astype(np.int32)
 
-    def prepare(self, rows: np.ndarray) -> tuple[int, int, int, int, int]:
-        """``rows``: [n_seg, 8] int64.  Returns (segs_ptr, chunks_ptr, n_seg, total_chunks, on_device)."""
+    def prepare(
+        self, rows: np.ndarray, chunk: Optional[int] = None, force_device: bool = False
+    ) -> tuple[int, int, int, int, int]:
+        """``rows``: [n_seg, 8] int64.  Returns (segs_ptr, chunks_ptr, n_seg, total_chunks, on_device).
+
+        ``chunk`` is the number of elements one CTA iteration of the target kernel covers
+        (default: the local step kernels'); ``force_device`` keeps even short tables on
+        the device (the peer kernels read their table from device memory only).
+        """
         n_seg = rows.shape[0]
-        chunk = native.chunk_elems()
+        chunk = chunk or native.chunk_elems()
         same_shape = self._host is not None and self._host.shape == rows.shape
         if not same_shape or not np.array_equal(self._host[:, 7], rows[:, 7]):
             self._chunks = self.chunk_prefix(rows[:, 7], chunk)
@@ -104,7 +111,7 @@ class SegmentTable:
         else:
             changed = not np.array_equal(self._host, rows)
         total = int(self._chunks[-1])
-        if n_seg <= native.FO_MAX_INLINE_SEGS:
+        if n_seg <= native.FO_MAX_INLINE_SEGS and not force_device:
             self._host = rows
             return rows.ctypes.data, self._chunks.ctypes.data, n_seg, total, 0
         if changed or self._dev is None:
@@ -166,6 +173,57 @@ def launch_momentum(
             ctypes.byref(h), native.stream_ptr(table.device),
         )
     native.check(rc, "fo_momentum_step")
+    global _launches
+    _launches += 1
+
+
+def launch_adam_peer(
+    table: SegmentTable,
+    rows: np.ndarray,
+    dtype: torch.dtype,
+    err_bytes: int,
+    quantized: bool,
+    hyper: AdamHyper,
+    comm: "native.FoCommArgs",
+) -> None:
+    """Adam/AdamW step whose gradients are averaged from every rank's symmetric buffer
+    inside the kernel; ``rows[:, 1]`` holds byte offsets into those buffers."""
+    if rows.shape[0] == 0:
+        return
+    lib = native.load()
+    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(), force_device=True)
+    h = hyper.to_c()
+    with torch.cuda.device(table.device):
+        rc = lib.fo_adam_step_peer(
+            segs, chunks, n_seg, total, native.DTYPE_CODE[dtype], err_bytes, int(quantized),
+            ctypes.byref(h), ctypes.byref(comm), native.stream_ptr(table.device),
+        )
+    native.check(rc, "fo_adam_step_peer")
+    global _launches
+    _launches += 1
+
+
+def launch_momentum_peer(
+    table: SegmentTable,
+    rows: np.ndarray,
+    dtype: torch.dtype,
+    err_bytes: int,
+    state_mode: int,
+    hyper: MomentumHyper,
+    comm: "native.FoCommArgs",
+) -> None:
+    """Lion / SGD / SGDW counterpart of :func:`launch_adam_peer`."""
+    if rows.shape[0] == 0:
+        return
+    lib = native.load()
+    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(), force_device=True)
+    h = hyper.to_c()
+    with torch.cuda.device(table.device):
+        rc = lib.fo_momentum_step_peer(
+            segs, chunks, n_seg, total, native.DTYPE_CODE[dtype], err_bytes, state_mode,
+            ctypes.byref(h), ctypes.byref(comm), native.stream_ptr(table.device),
+        )
+    native.check(rc, "fo_momentum_step_peer")
     global _launches
     _launches += 1
 

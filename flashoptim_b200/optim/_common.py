@@ -27,14 +27,18 @@ def err_bytes_of(state: dict[str, Any]) -> int:
 
 
 def pack_rows(
-    items: list[tuple[torch.Tensor, torch.Tensor, dict[str, Any]]], state_keys: tuple[str, ...]
+    items: list[tuple[torch.Tensor, Any, dict[str, Any]]], state_keys: tuple[str, ...]
 ) -> np.ndarray:
-    """[n, 8] int64 segment image (see ``csrc/fo_api.h``: p, g, ecc, s0, s0s, s1, s1s, n)."""
+    """[n, 8] int64 segment image (see ``csrc/fo_api.h``: p, g, ecc, s0, s0s, s1, s1s, n).
+
+    The gradient entry of an item is a tensor (local steps) or an ``int`` byte offset
+    into the ranks' symmetric gradient buffers (steps fused with the collective).
+    """
     rows = np.zeros((len(items), SEG_WORDS), dtype=np.int64)
     for i, (p, g, st) in enumerate(items):
         r = rows[i]
         r[0] = p.data_ptr()
-        r[1] = g.data_ptr()
+        r[1] = g if isinstance(g, int) else g.data_ptr()
         e = st.get("error_bits")
         if e is not None:
             r[2] = e.data_ptr()

@@ -8,7 +8,7 @@ from typing import Any, Iterable, Literal, Optional
 import torch
 
 from ..ops import oracle
-from ..ops.step import AdamHyper, launch_adam
+from ..ops.step import AdamHyper, launch_adam, launch_adam_peer
 from ._common import err_bytes_of, pack_rows, write_back
 from .base import FlashOptimizer
 from .state import QuantizedTensorSpec
@@ -104,7 +104,7 @@ class FlashAdam(FlashOptimizer):
         m_state.set_data(m32)
         v_state.set_data(v32)
 
-    def _fused_step(self, items, hparams, group_index) -> None:
+    def _fused_step(self, items, hparams, group_index, peer=None) -> None:
         buckets: dict[Any, list] = defaultdict(list)
         for it in items:
             p, _, st = it
@@ -122,8 +122,14 @@ class FlashAdam(FlashOptimizer):
                 step=step,
                 decoupled=self._decoupled,
             )
-            table = self._table((group_index, device, dtype, err, quantized, len(bucket)), device)
-            launch_adam(table, pack_rows(bucket, ("exp_avg", "exp_avg_sq")), dtype, err, quantized, hyper)
+            rows = pack_rows(bucket, ("exp_avg", "exp_avg_sq"))
+            if peer is None:
+                table = self._table((group_index, device, dtype, err, quantized, len(bucket)), device)
+                launch_adam(table, rows, dtype, err, quantized, hyper)
+            else:
+                hyper.grad_scale = peer.grad_scale
+                table = self._table(("peer", peer.key, group_index, dtype, err, quantized, len(bucket)), device)
+                launch_adam_peer(table, rows, dtype, err, quantized, hyper, peer.next_args())
 
 
 class FlashAdamW(FlashAdam):

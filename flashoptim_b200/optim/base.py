@@ -130,6 +130,11 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         self._transient_state: dict[int, dict[str, Any]] = {}
         # device segment tables of the fused launches, keyed by bucket
         self._tables: dict[Any, SegmentTable] = {}
+        # parameters already updated during this backward by a kernel fused with the
+        # gradient collective (see flashoptim_b200.parallel); the next step()/step_param()
+        # skips them once
+        self._peer_stepped: set[int] = set()
+        self._post_step_callbacks: list[Callable[[], None]] = []
 
         defaults = dict(defaults or {})
         defaults.update({"lr": lr, "master_bytewidth": master_bytewidth, "quantize": quantize})
@@ -199,11 +204,16 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
     @abc.abstractmethod
     def _fused_step(
         self,
-        items: list[tuple[torch.Tensor, torch.Tensor, dict[str, Any]]],
+        items: list[tuple[torch.Tensor, Any, dict[str, Any]]],
         hparams: dict[str, Any],
         group_index: int,
+        peer: Any = None,
     ) -> None:
-        """Update a list of (local param, local grad, state) on CUDA with fused kernels."""
+        """Update a list of (local param, local grad, state) on CUDA with fused kernels.
+
+        With ``peer`` (a :class:`flashoptim_b200.parallel.symm.PeerGradients`) the
+        gradient entries are byte offsets into the ranks' symmetric buffers and the
+        kernels average them over NVLink while updating."""
 
     def _initial_value_for_state_var(self, param: torch.Tensor, key: str) -> torch.Tensor:
         del key
@@ -328,6 +338,9 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         fused_items: list[tuple[torch.Tensor, torch.Tensor, dict[str, Any]]] = []
         for p in params:
             self._ensure_state_initialized(p, group)
+            if self._peer_stepped and id(p) in self._peer_stepped:
+                self._peer_stepped.discard(id(p))  # updated inside the collective already
+                continue
             # zero-sized shards and frozen parameters keep their (empty) state: DCP
             # expects a state entry for every parameter of every group
             if p.numel() < 1 or not p.requires_grad or p.grad is None:
@@ -389,7 +402,40 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
                 loss = closure()
         for gi, group in enumerate(self.param_groups):
             self._step_group(group["params"], group, gi)
+        for fn in self._post_step_callbacks:
+            fn()
         return loss
+
+    @torch.no_grad()
+    def step_from_peers(self, params: list[torch.Tensor], peer: Any) -> None:
+        """Update ``params`` from gradients that still sit, unreduced, in every rank's
+        symmetric buffer (``peer.offsets[id(local tensor)]`` = byte offset of each one).
+
+        The launches run on the current stream.  Each parameter is marked so that the
+        following ``step()`` / ``step_param()`` leaves it alone once.
+        """
+        by_group: dict[int, list[torch.Tensor]] = {}
+        index_of = {id(p): gi for gi, g in enumerate(self.param_groups) for p in g["params"]}
+        for p in params:
+            by_group.setdefault(index_of[id(p)], []).append(p)
+        for gi, plist in by_group.items():
+            group = self.param_groups[gi]
+            items = []
+            for p in plist:
+                self._ensure_state_initialized(p, group)
+                p_local = local_tensor(p)
+                if p_local.numel() < 1 or not p.requires_grad:
+                    continue
+                if not (p_local.is_cuda and p_local.is_contiguous()):
+                    raise RuntimeError("steps fused with the collective need contiguous CUDA parameters")
+                if self._check_numerics:
+                    self._check_param_numerics(p, group["lr"], group["master_bytewidth"])
+                state = self.state[p]
+                self._pre_step(state)
+                items.append((p_local, int(peer.offsets[id(p_local)]), state))
+                self._peer_stepped.add(id(p))
+            if items:
+                self._fused_step(items, group, gi, peer=peer)
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         if self._gradient_release:
@@ -523,6 +569,8 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         super().__setstate__(state)
         self.__dict__.setdefault("_tables", {})
         self.__dict__.setdefault("_transient_state", {})
+        self.__dict__.setdefault("_peer_stepped", set())
+        self.__dict__.setdefault("_post_step_callbacks", [])
         self._tables.clear()
         self._transient_state.clear()
         opt_state = cast(dict[torch.Tensor, Any], state["state"])

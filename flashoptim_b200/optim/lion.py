@@ -8,7 +8,7 @@ from typing import Any, Iterable, Literal, Optional
 import torch
 
 from ..ops import native, oracle
-from ..ops.step import MomentumHyper, launch_momentum
+from ..ops.step import MomentumHyper, launch_momentum, launch_momentum_peer
 from ._common import err_bytes_of, pack_rows, state_mode, write_back
 from .base import FlashOptimizer
 from .state import QuantizedTensorSpec
@@ -81,12 +81,18 @@ class FlashLion(FlashOptimizer):
         write_back(param, p32, errors, hparams["master_bytewidth"])
         m_state.set_data(m32)
 
-    def _fused_step(self, items, hparams, group_index) -> None:
+    def _fused_step(self, items, hparams, group_index, peer=None) -> None:
         buckets: dict[Any, list] = defaultdict(list)
         for it in items:
             p, _, st = it
             buckets[(p.device, p.dtype, err_bytes_of(st), state_mode(st, "exp_avg"))].append(it)
         h = self._hyper(hparams)
         for (device, dtype, err, mode), bucket in buckets.items():
-            table = self._table((group_index, device, dtype, err, mode, len(bucket)), device)
-            launch_momentum(table, pack_rows(bucket, ("exp_avg",)), dtype, err, mode, h)
+            rows = pack_rows(bucket, ("exp_avg",))
+            if peer is None:
+                table = self._table((group_index, device, dtype, err, mode, len(bucket)), device)
+                launch_momentum(table, rows, dtype, err, mode, h)
+            else:
+                h.grad_scale = peer.grad_scale
+                table = self._table(("peer", peer.key, group_index, dtype, err, mode, len(bucket)), device)
+                launch_momentum_peer(table, rows, dtype, err, mode, h, peer.next_args())

@@ -8,7 +8,7 @@ from typing import Any, Iterable, Literal, Optional
 import torch
 
 from ..ops import native, oracle
-from ..ops.step import MomentumHyper, launch_momentum
+from ..ops.step import MomentumHyper, launch_momentum, launch_momentum_peer
 from ._common import err_bytes_of, pack_rows, state_mode, write_back
 from .base import FlashOptimizer
 from .state import QuantizedTensorSpec
@@ -91,7 +91,7 @@ class FlashSGD(FlashOptimizer):
         if use_mom:
             m_state.set_data(m32)
 
-    def _fused_step(self, items, hparams, group_index) -> None:
+    def _fused_step(self, items, hparams, group_index, peer=None) -> None:
         h = self._hyper(hparams)
         key_name = "momentum_buffer" if h.mom_coef != 0.0 else None
         buckets: dict[Any, list] = defaultdict(list)
@@ -100,8 +100,14 @@ class FlashSGD(FlashOptimizer):
             buckets[(p.device, p.dtype, err_bytes_of(st), state_mode(st, key_name))].append(it)
         for (device, dtype, err, mode), bucket in buckets.items():
             keys = ("momentum_buffer",) if mode != native.FO_STATE_NONE else ()
-            table = self._table((group_index, device, dtype, err, mode, len(bucket)), device)
-            launch_momentum(table, pack_rows(bucket, keys), dtype, err, mode, h)
+            rows = pack_rows(bucket, keys)
+            if peer is None:
+                table = self._table((group_index, device, dtype, err, mode, len(bucket)), device)
+                launch_momentum(table, rows, dtype, err, mode, h)
+            else:
+                h.grad_scale = peer.grad_scale
+                table = self._table(("peer", peer.key, group_index, dtype, err, mode, len(bucket)), device)
+                launch_momentum_peer(table, rows, dtype, err, mode, h, peer.next_args())
 
 
 class FlashSGDW(FlashSGD):

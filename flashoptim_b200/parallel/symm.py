@@ -1,0 +1,194 @@
+"""Symmetric NVLink buffers and the flag protocol of the peer kernels.
+
+A :class:`PeerGroup` is the set of GPUs of one node that map each other's
+buffers (allocation and handle exchange through
+``torch.distributed._symmetric_memory``; all data movement is done by this
+library's kernels).  It owns
+
+* a *signal pad*: ``channels x 8`` uint32 flags per rank, written by peers with
+  release stores and read with acquire loads, carrying monotonically growing
+  epochs;
+* a 4-word local *status* tensor where a kernel records a wait that ran out;
+* any number of :class:`SymmBuffer` allocations.
+
+Ordering protocol for a buffer with channels (ready, done) and epoch ``e``:
+a consumer kernel publishes ``ready = e`` ("my copy of the buffer is written",
+true by stream order), waits until every rank has published it, reads all
+copies, and finally publishes ``done = e``.  Before a rank overwrites its copy
+again it waits (``wait_done``) until every rank has published ``done = e``.
+
+With ``world_size == 1`` no symmetric allocation is needed and ordinary tensors
+are used, which also lets one process emulate several ranks for tests by
+passing explicit buffer lists.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+CHANNELS = 64
+
+
+class CommTimeoutError(RuntimeError):
+    """A device-side wait for another rank's flag ran out of time."""
+
+
+class SymmBuffer:
+    """``nbytes`` of device memory mapped on every rank of a :class:`PeerGroup`."""
+
+    def __init__(self, tensor: torch.Tensor, ptrs: Sequence[int], multicast_ptr: int, handle=None):
+        self.tensor = tensor          # this rank's copy, flat uint8
+        self.ptrs = list(ptrs)        # address of every rank's copy in this process
+        self.multicast_ptr = multicast_ptr
+        self._handle = handle         # keeps the mapping alive
+
+    @property
+    def nbytes(self) -> int:
+        return self.tensor.numel()
+
+    def view(self, offset: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """This rank's copy, ``numel`` elements of ``dtype`` starting ``offset`` bytes in."""
+        size = numel * torch.empty((), dtype=dtype).element_size()
+        return self.tensor[offset:offset + size].view(dtype)
+
+
+class PeerGroup:
+    def __init__(
+        self,
+        group: Optional[dist.ProcessGroup] = None,
+        device: Optional[torch.device] = None,
+        timeout_s: float = 2.0,
+        use_multicast: bool = True,
+    ):
+        self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
+        self.world = dist.get_world_size(self.group) if self.group is not None else 1
+        self.rank = dist.get_rank(self.group) if self.group is not None else 0
+        if self.world > native.FO_MAX_PEERS:
+            raise ValueError(f"at most {native.FO_MAX_PEERS} ranks (one NVSwitch node) are supported")
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.use_multicast = use_multicast
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._pad = self.allocate(CHANNELS * native.FO_MAX_PEERS * 4, zero=True)
+        self._next_channel = 0
+
+    # ------------------------------------------------------------------ allocation
+    def allocate(self, nbytes: int, zero: bool = False) -> SymmBuffer:
+        """Collective: every rank must call with the same size, in the same order."""
+        nbytes = (int(nbytes) + 255) // 256 * 256
+        if self.world == 1:
+            t = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            if zero:
+                t.zero_()
+            return SymmBuffer(t, [t.data_ptr()], 0)
+        import torch.distributed._symmetric_memory as symm_mem
+
+        t = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        if zero:
+            t.zero_()
+        hdl = symm_mem.rendezvous(t, group=self.group)
+        mc = int(hdl.multicast_ptr) if (self.use_multicast and hdl.has_multicast_support) else 0
+        buf = SymmBuffer(t, [int(p) for p in hdl.buffer_ptrs], mc, hdl)
+        if zero:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+        return buf
+
+    def new_channels(self) -> tuple[int, int]:
+        """A fresh (ready, done) channel pair; same sequence on every rank."""
+        if self._next_channel + 2 > CHANNELS:
+            raise RuntimeError("out of signal channels")
+        c = self._next_channel
+        self._next_channel += 2
+        return c, c + 1
+
+    # ------------------------------------------------------------------ kernel arguments
+    def comm_args(
+        self,
+        buf: SymmBuffer,
+        epoch: int,
+        ready_channel: int,
+        done_channel: int,
+        grad_out: Optional[torch.Tensor] = None,
+        grad_out_sub: int = 0,
+        multicast: Optional[bool] = None,
+        pads: Optional[Sequence[int]] = None,
+        ptrs: Optional[Sequence[int]] = None,
+        world: Optional[int] = None,
+        rank: Optional[int] = None,
+    ) -> native.FoCommArgs:
+        a = native.FoCommArgs()
+        ptrs = list(ptrs if ptrs is not None else buf.ptrs)
+        pads = list(pads if pads is not None else self._pad.ptrs)
+        w = world if world is not None else self.world
+        for r in range(w):
+            a.grad[r] = ptrs[r]
+            a.pad[r] = pads[r]
+        use_mc = self.use_multicast if multicast is None else multicast
+        a.multicast = buf.multicast_ptr if (use_mc and buf.multicast_ptr) else None
+        a.status = self.status.data_ptr()
+        a.grad_out = grad_out.data_ptr() if grad_out is not None else None
+        a.grad_out_sub = grad_out_sub
+        a.timeout_ns = self.timeout_ns
+        a.epoch = epoch & 0xFFFFFFFF
+        a.world = w
+        a.rank = rank if rank is not None else self.rank
+        a.ready_channel = ready_channel
+        a.done_channel = done_channel
+        return a
+
+    # ------------------------------------------------------------------ flags
+    def wait(self, args: native.FoCommArgs, channel: int) -> None:
+        """Enqueue (current stream) a bounded wait until every rank's ``channel`` flag reached ``args.epoch``."""
+        native.check(native.load().fo_comm_wait(ctypes.byref(args), channel, native.stream_ptr(self.device)),
+                     "fo_comm_wait")
+
+    def signal(self, args: native.FoCommArgs, channel: int) -> None:
+        native.check(native.load().fo_comm_signal(ctypes.byref(args), channel, native.stream_ptr(self.device)),
+                     "fo_comm_signal")
+
+    def check_status(self) -> None:
+        """Synchronise and raise :class:`CommTimeoutError` if any device-side wait ran out."""
+        torch.cuda.synchronize(self.device)
+        st = self.status.tolist()
+        if st[0] != 0:
+            self.status.zero_()
+            raise CommTimeoutError(
+                f"rank {self.rank}: wait on channel mask {st[0]:#x} timed out (missing rank {st[1] - 1})"
+            )
+
+
+@dataclass
+class PeerGradients:
+    """What an optimizer needs to step straight from the ranks' symmetric gradient buffers."""
+
+    group: PeerGroup
+    buf: SymmBuffer
+    ready_channel: int
+    done_channel: int
+    offsets: dict[int, int] = field(default_factory=dict)  # id(local param tensor) -> byte offset
+    grad_scale: float = 1.0
+    grad_out: Optional[torch.Tensor] = None
+    grad_out_sub: int = 0
+    key: int = 0
+    epoch: int = 0  # last epoch used on this buffer
+
+    def next_args(self) -> native.FoCommArgs:
+        self.epoch += 1
+        return self.group.comm_args(
+            self.buf, self.epoch, self.ready_channel, self.done_channel, self.grad_out, self.grad_out_sub
+        )
+
+    def wait_done(self) -> None:
+        """Current stream waits until every rank has finished reading the buffer's last use."""
+        if self.epoch == 0 or self.group.world == 1:
+            return
+        args = self.group.comm_args(self.buf, self.epoch, self.ready_channel, self.done_channel)
+        self.group.wait(args, self.done_channel)
