@@ -189,7 +189,8 @@ def main():
         try:
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
-            fused_comm = fo_fsdp.enable_fused_fsdp(model, opt)
+            fused_state = fo_fsdp.enable_fused_fsdp(model, opt)
+            fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
             if rank == 0:
                 print(f"[bench] fused FSDP path not enabled: {e}", file=sys.stderr)

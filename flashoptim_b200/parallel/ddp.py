@@ -1,0 +1,124 @@
+"""DistributedDataParallel with the bucket all-reduce fused into the optimizer update.
+
+``fuse_ddp_allreduce(ddp_model, optimizer)`` registers a DDP communication hook.
+When a gradient bucket is ready the hook copies it into this rank's slice of a
+symmetric NVLink arena and, on a side stream, launches one kernel that reads
+the matching slice of every rank, averages in fp32 in rank order (all replicas
+therefore compute bit-identical values) and applies the optimizer update to the
+bucket's parameters and replicated states in the same pass.  NCCL is not
+involved; the averaged gradient never exists in HBM unless ``write_back=True``.
+
+The reference cannot step inside a DDP hook at all (it rejects gradient release
+for DDP, ``flashoptim/optimizers.py:3111-3123``): PyTorch's reducer owns the
+bucket and an update there serialises its pipeline.  Here the update runs on
+its own stream from a private copy of the bucket, and ``optimizer.step()``
+afterwards only skips the parameters that were already updated and joins the
+side stream.  Plain DDP (no hook) with ``optimizer.step()`` keeps working.
+
+Gradient accumulation with ``no_sync()`` is transparent: DDP does not call the
+hook on unsynchronised backwards and the bucket later holds the accumulated sum.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch.nn.parallel import DistributedDataParallel as DDP
+
+from ..optim.base import FlashOptimizer
+from .symm import PeerGradients, PeerGroup
+
+
+class FusedDDPState:
+    def __init__(
+        self,
+        ddp_model: DDP,
+        optimizer: FlashOptimizer,
+        group: Optional[dist.ProcessGroup] = None,
+        timeout_s: float = 5.0,
+        use_multicast: bool = False,
+        write_back: bool = False,
+    ):
+        params = [p for p in ddp_model.parameters() if p.requires_grad]
+        if not params:
+            raise ValueError("model has no trainable parameters")
+        if any(not p.is_cuda for p in params):
+            raise ValueError("the fused DDP path needs CUDA parameters")
+        self.optimizer = optimizer
+        self.write_back = write_back
+        self.peers = PeerGroup(group, device=params[0].device, timeout_s=timeout_s, use_multicast=use_multicast)
+        # every bucket gets a 256-byte aligned slice; one slice per parameter is the worst case
+        total = sum(p.numel() * p.element_size() for p in params) + 256 * (len(params) + 1)
+        self.arena = self.peers.allocate(total)
+        ready, done = self.peers.new_channels()
+        self.grads = PeerGradients(self.peers, self.arena, ready, done, grad_scale=1.0 / self.peers.world, key=id(self))
+        self.side = torch.cuda.Stream(device=params[0].device)
+        self.cursor = 0
+        self.region_epoch: dict[int, int] = {}
+        self.buckets_fused = 0
+        optimizer._post_step_callbacks.append(self._join)
+
+    def _join(self) -> None:
+        torch.cuda.current_stream().wait_stream(self.side)
+
+    def hook(self, _state, bucket):  # no annotations: DDP compares them to the classes themselves
+        buf = bucket.buffer()
+        if bucket.index() == 0:
+            self.cursor = 0
+        nbytes = buf.numel() * buf.element_size()
+        off = self.cursor
+        self.cursor += (nbytes + 255) // 256 * 256
+        if self.cursor > self.arena.nbytes:
+            raise RuntimeError("gradient buckets exceed the symmetric arena")
+        cur = torch.cuda.current_stream()
+        # peers must have finished reading what this region held in the previous step
+        last = self.region_epoch.get(off, 0)
+        if last and self.peers.world > 1:
+            args = self.peers.comm_args(self.arena, last, self.grads.ready_channel, self.grads.done_channel)
+            self.peers.wait(args, self.grads.done_channel)
+        self.arena.view(off, buf.numel(), buf.dtype).copy_(buf)
+        self.side.wait_event(cur.record_event())
+        params = bucket.parameters()
+        base = buf.data_ptr()
+        self.grads.offsets = {id(p): off + (g.data_ptr() - base) for p, g in zip(params, bucket.gradients())}
+        if self.write_back:
+            self.grads.grad_out, self.grads.grad_out_sub = buf, off
+        with torch.cuda.stream(self.side):
+            self.optimizer.step_from_peers(list(params), self.grads)
+        self.region_epoch[off] = self.grads.epoch
+        self.buckets_fused += 1
+        fut: torch.futures.Future = torch.futures.Future()
+        fut.set_result(buf)
+        return fut
+
+    def check(self) -> None:
+        """Synchronise and raise if a device-side wait for another rank timed out."""
+        self.peers.check_status()
+
+
+def fuse_ddp_allreduce(
+    ddp_model: DDP,
+    optimizer: FlashOptimizer,
+    *,
+    group: Optional[dist.ProcessGroup] = None,
+    timeout_s: float = 5.0,
+    use_multicast: bool = False,
+    write_back: bool = False,
+) -> FusedDDPState:
+    """Fuse DDP's per-bucket gradient all-reduce with ``optimizer``'s update.
+
+    Collective: call on every rank, after constructing ``ddp_model`` (with
+    ``gradient_as_bucket_view=True``) and ``optimizer``.  Keep calling
+    ``optimizer.step()`` / ``zero_grad()`` as usual: parameters updated by the hook
+    are skipped there.  ``write_back=True`` also stores the averaged gradient back
+    into the bucket (needed only if something else reads ``p.grad``).
+    ``use_multicast`` fetches through NVSwitch ``multimem.ld_reduce``; the default
+    uses peer loads in rank order, which guarantees bit-identical replicas.
+    """
+    if not isinstance(ddp_model, DDP):
+        raise TypeError("fuse_ddp_allreduce expects a DistributedDataParallel model")
+    state = FusedDDPState(ddp_model, optimizer, group, timeout_s, use_multicast, write_back)
+    ddp_model.register_comm_hook(state, state.hook)
+    return state

@@ -1,0 +1,166 @@
+"""FSDP2 (``fully_shard``) with the gradient reduce-scatter fused into the sharded update.
+
+``enable_fused_fsdp(model, optimizer)`` installs a custom reduce-scatter
+communicator on every FSDP module (``FSDPModule.set_custom_reduce_scatter``).
+FSDP2 lays a parameter group's unsharded gradients out as a ``[world, shard]``
+matrix; that matrix is allocated inside a symmetric NVLink buffer, and when
+FSDP2 asks for the reduce-scatter, rank ``r`` launches ONE kernel that reads row
+``r`` of every rank, averages in fp32 and applies the optimizer update to its
+shards of the group's parameters in the same pass.  The averaged shard is also
+written to FSDP2's reduce-scatter output so that ``param.grad`` stays meaningful.
+The kernel runs on FSDP2's reduce-scatter stream, overlapped with backward
+compute, exactly where the reference's gradient-release hook would have run its
+per-tensor update after NCCL finished (``flashoptim/optimizers.py:3040-3047``).
+
+Parameters updated this way are skipped once by the next ``step()`` /
+``step_param()``, so the usual training loop and gradient release keep working.
+Groups the kernel cannot serve (non-default divide factors, a reduce dtype
+different from the parameters, shards along a non-zero dimension, parameters
+without gradients) fall back to NCCL for that call.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..optim.base import FlashOptimizer, local_tensor
+from .symm import PeerGradients, PeerGroup
+
+try:  # torch >= 2.8
+    from torch.distributed.fsdp import FSDPModule
+    from torch.distributed.fsdp._fully_shard._fsdp_api import ReduceScatter
+except Exception:  # pragma: no cover
+    FSDPModule = None  # type: ignore[assignment]
+    ReduceScatter = object  # type: ignore[assignment,misc]
+
+
+class _Pool:
+    """Round-robin pool of symmetric reduce-scatter input buffers shared by all groups."""
+
+    def __init__(self, peers: PeerGroup, nbytes: int, depth: int):
+        self.slots = []
+        for i in range(depth):
+            buf = peers.allocate(nbytes)
+            ready, done = peers.new_channels()
+            self.slots.append(PeerGradients(peers, buf, ready, done, grad_scale=1.0 / peers.world, key=i))
+        self._next = 0
+
+    def take(self) -> PeerGradients:
+        s = self.slots[self._next]
+        self._next = (self._next + 1) % len(self.slots)
+        return s
+
+
+class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
+    def __init__(self, ctx: "FusedFSDPState", fsdp_params: list) -> None:
+        self.ctx = ctx
+        self.fsdp_params = fsdp_params
+        self._slot: Optional[PeerGradients] = None
+        w = ctx.peers.world
+        self.row_numels = [fp.padded_sharded_param_size.numel() for fp in fsdp_params]
+        self.input_numel = w * sum(self.row_numels)
+        self.dtype = fsdp_params[0].sharded_param.dtype
+        owned = {id(p) for g in ctx.optimizer.param_groups for p in g["params"]}
+        self.supported = all(
+            fp.sharded_param.dtype == self.dtype and getattr(fp.fsdp_placement, "dim", 0) == 0
+            and not fp.offload_to_cpu and id(fp.sharded_param) in owned and fp.sharded_param.requires_grad
+            for fp in fsdp_params
+        )
+
+    # FSDP2 calls allocate() for the reduce-scatter input (on the compute stream, right
+    # before it packs the gradients) and then for the output (on the reduce-scatter stream).
+    def allocate(self, size, *, dtype, device):
+        numel = int(size[0])
+        esize = torch.empty((), dtype=dtype).element_size()
+        if (self.supported and numel == self.input_numel and dtype == self.dtype
+                and numel * esize <= self.ctx.pool_bytes):
+            slot = self.ctx.pool.take()
+            slot.wait_done()  # every rank is done reading this buffer's previous contents
+            self._slot = slot
+            return slot.buf.view(0, numel, dtype)
+        return torch.empty(*size, dtype=dtype, device=device)
+
+    def __call__(self, output_tensor, input_tensor, group, op, async_op=False):
+        slot, self._slot = self._slot, None
+        fused = (
+            slot is not None
+            and input_tensor.data_ptr() == slot.buf.tensor.data_ptr()
+            and op == dist.ReduceOp.AVG
+            and not async_op
+        )
+        if not fused:
+            self.ctx.fallbacks += 1
+            return dist.reduce_scatter_tensor(output=output_tensor, input=input_tensor, group=group, op=op,
+                                              async_op=async_op)
+        peers = self.ctx.peers
+        esize = input_tensor.element_size()
+        row_bytes = sum(self.row_numels) * esize
+        base = peers.rank * row_bytes
+        offsets, off = {}, 0
+        for fp, n in zip(self.fsdp_params, self.row_numels):
+            offsets[id(local_tensor(fp.sharded_param))] = base + off
+            off += n * esize
+        slot.offsets = offsets
+        slot.grad_out, slot.grad_out_sub = output_tensor, base
+        self.ctx.optimizer.step_from_peers([fp.sharded_param for fp in self.fsdp_params], slot)
+        self.ctx.fused_calls += 1
+        return None
+
+
+class FusedFSDPState:
+    def __init__(self, model: nn.Module, optimizer: FlashOptimizer, group, timeout_s, use_multicast, depth):
+        self.optimizer = optimizer
+        modules = [m for m in model.modules() if FSDPModule is not None and isinstance(m, FSDPModule)]
+        if not modules:
+            raise ValueError("model has no fully_shard-ed modules")
+        groups = []
+        for m in modules:
+            pg = m._get_fsdp_state()._fsdp_param_group
+            if pg is not None and pg.fsdp_params:
+                groups.append((m, pg))
+        if not groups:
+            raise ValueError("no FSDP parameter groups found")
+        mesh_group = groups[0][1]._reduce_scatter_process_group
+        self.peers = PeerGroup(group or mesh_group, device=groups[0][1].device, timeout_s=timeout_s,
+                               use_multicast=use_multicast)
+        self.fused_calls = 0
+        self.fallbacks = 0
+        self.comms = []
+        need = 0
+        for m, pg in groups:
+            comm = FusedReduceScatter(self, list(pg.fsdp_params))
+            need = max(need, comm.input_numel * torch.empty((), dtype=comm.dtype).element_size())
+            self.comms.append((m, comm))
+        self.pool_bytes = need
+        self.pool = _Pool(self.peers, need, depth)
+        for m, comm in self.comms:
+            m.set_custom_reduce_scatter(comm)
+
+    def check(self) -> None:
+        self.peers.check_status()
+
+
+def enable_fused_fsdp(
+    model: nn.Module,
+    optimizer: FlashOptimizer,
+    *,
+    group: Optional[dist.ProcessGroup] = None,
+    timeout_s: float = 5.0,
+    use_multicast: bool = False,
+    depth: int = 2,
+) -> Optional[FusedFSDPState]:
+    """Fuse FSDP2's gradient reduce-scatter with ``optimizer``'s sharded update.
+
+    Collective: call on every rank after ``fully_shard`` and after constructing the
+    optimizer.  Returns the state object (``.fused_calls`` / ``.fallbacks`` count what
+    happened; ``.check()`` raises if a device-side wait timed out), or ``None`` when the
+    data-parallel group has a single rank (FSDP2 then performs no reduce-scatter).
+    ``depth`` symmetric buffers of the largest group's gradient size are kept.
+    """
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return None
+    return FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth)
