@@ -49,6 +49,9 @@ def parse_args():
     ap.add_argument("--activation-checkpointing", action="store_true")
     ap.add_argument("--fused-comm", default="auto", choices=["auto", "off"],
                     help="ours only: fuse the FSDP2 collectives with the update where supported")
+    ap.add_argument("--comm-ctas", type=int, default=0, help="grid cap of the fused reduce-scatter kernel")
+    ap.add_argument("--no-multicast", action="store_true",
+                    help="fused path: sum peer loads in fp32 instead of NVSwitch multimem.ld_reduce")
     return ap.parse_args()
 
 
@@ -189,7 +192,7 @@ def main():
         try:
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
-            fused_state = fo_fsdp.enable_fused_fsdp(model, opt)
+            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, max_ctas=args.comm_ctas, use_multicast=not args.no_multicast)
             fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
             if rank == 0:
@@ -278,6 +281,7 @@ def main():
                 "model": args.model, "n_params": n_params, "global_batch": world * b, "seq_len": s,
                 "parallelism": f"fsdp2x{world}", "optimizer": f"FlashAdamW mwb={mwb}",
                 "gradient_release": bool(args.gradient_release), "fused_comm": bool(fused_comm),
+                "fused_comm_multicast": bool(fused_comm and not args.no_multicast),
                 "activation_checkpointing": bool(cfg.activation_checkpointing),
                 "l2": "working set (>= 16 GB of weights) far exceeds the 126 MB L2; no flush",
             },

@@ -118,6 +118,8 @@ enum { FO_MAX_PEERS = 8 };
 //   grad_out     optional: the averaged gradient is also written to
 //                grad_out + (FoSeg.g + unit offset - grad_out_sub)
 //   timeout_ns   limit of every device-side wait
+//   max_ctas     cap on the number of CTAs, so that a link-bound kernel running beside
+//                backward leaves the SMs to the GEMMs
 typedef struct FoCommArgs {
   const void* grad[FO_MAX_PEERS];
   const void* multicast;
@@ -129,6 +131,7 @@ typedef struct FoCommArgs {
   uint32_t epoch;
   int world, rank;
   int ready_channel, done_channel;
+  int max_ctas;  // upper bound on the launch grid (0: fill the GPU); NVLink-bound work needs few SMs
 } FoCommArgs;
 
 // Elements per CTA iteration of the peer kernels (for the chunk prefix).

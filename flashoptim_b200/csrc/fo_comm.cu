@@ -325,11 +325,12 @@ __global__ void wait_kernel(const __grid_constant__ FoCommArgs A, int channel) {
   if (threadIdx.x < A.world) wait_flag(A, channel, threadIdx.x, A.epoch);
 }
 
-static int comm_grid(int64_t work_ctas) {
+static int comm_grid(int64_t work_ctas, const FoCommArgs* a) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   int64_t g = (int64_t)sms * kCommCtasPerSm;
+  if (a && a->max_ctas > 0 && a->max_ctas < g) g = a->max_ctas;
   if (work_ctas < g) g = work_ctas;
   return g < 1 ? 1 : (int)g;
 }
@@ -393,7 +394,7 @@ extern "C" int fo_adam_step_peer(const FoSeg* segs, const int32_t* chunk_begin, 
                                  const FoCommArgs* comm, void* stream) {
   if (!fo::args_ok(comm) || !hyper) return (int)cudaErrorInvalidValue;
   if (n_seg <= 0 || total_chunks <= 0) return 0;
-  const int grid = fo::comm_grid(total_chunks);
+  const int grid = fo::comm_grid(total_chunks, comm);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case FO_BF16:
@@ -414,7 +415,7 @@ extern "C" int fo_momentum_step_peer(const FoSeg* segs, const int32_t* chunk_beg
                                      const FoMomentumHyper* hyper, const FoCommArgs* comm, void* stream) {
   if (!fo::args_ok(comm) || !hyper) return (int)cudaErrorInvalidValue;
   if (n_seg <= 0 || total_chunks <= 0) return 0;
-  const int grid = fo::comm_grid(total_chunks);
+  const int grid = fo::comm_grid(total_chunks, comm);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case FO_BF16:
@@ -434,7 +435,7 @@ extern "C" int fo_reduce_peer(int64_t n, int64_t src_offset_bytes, void* out, in
                               const FoCommArgs* comm, void* stream) {
   if (!fo::args_ok(comm)) return (int)cudaErrorInvalidValue;
   if (n <= 0) return 0;
-  const int grid = fo::comm_grid((n + fo::kCommChunk - 1) / fo::kCommChunk);
+  const int grid = fo::comm_grid((n + fo::kCommChunk - 1) / fo::kCommChunk, comm);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case FO_BF16:
@@ -455,7 +456,7 @@ extern "C" int fo_reduce_peer(int64_t n, int64_t src_offset_bytes, void* out, in
 extern "C" int fo_allgather_peer(int64_t slot_bytes, const FoCommArgs* comm, void* stream) {
   if (!fo::args_ok(comm) || slot_bytes < 0 || (slot_bytes & 15)) return (int)cudaErrorInvalidValue;
   if (slot_bytes == 0) return 0;
-  const int grid = fo::comm_grid((slot_bytes / 16 + fo::kCommThreads - 1) / fo::kCommThreads);
+  const int grid = fo::comm_grid((slot_bytes / 16 + fo::kCommThreads - 1) / fo::kCommThreads, comm);
   fo::allgather_pull_kernel<<<grid, fo::kCommThreads, 0, static_cast<cudaStream_t>(stream)>>>(slot_bytes, *comm);
   return (int)cudaGetLastError();
 }

@@ -86,6 +86,7 @@ class FoCommArgs(Structure):
         ("rank", c_int),
         ("ready_channel", c_int),
         ("done_channel", c_int),
+        ("max_ctas", c_int),
     ]
 
 

@@ -112,7 +112,8 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
 
 
 class FusedFSDPState:
-    def __init__(self, model: nn.Module, optimizer: FlashOptimizer, group, timeout_s, use_multicast, depth):
+    def __init__(self, model: nn.Module, optimizer: FlashOptimizer, group, timeout_s, use_multicast, depth,
+                 max_ctas=0):
         self.optimizer = optimizer
         modules = [m for m in model.modules() if FSDPModule is not None and isinstance(m, FSDPModule)]
         if not modules:
@@ -126,7 +127,7 @@ class FusedFSDPState:
             raise ValueError("no FSDP parameter groups found")
         mesh_group = groups[0][1]._reduce_scatter_process_group
         self.peers = PeerGroup(group or mesh_group, device=groups[0][1].device, timeout_s=timeout_s,
-                               use_multicast=use_multicast)
+                               use_multicast=use_multicast, max_ctas=max_ctas)
         self.fused_calls = 0
         self.fallbacks = 0
         self.comms = []
@@ -152,6 +153,7 @@ def enable_fused_fsdp(
     timeout_s: float = 5.0,
     use_multicast: bool = False,
     depth: int = 2,
+    max_ctas: int = 0,
 ) -> Optional[FusedFSDPState]:
     """Fuse FSDP2's gradient reduce-scatter with ``optimizer``'s sharded update.
 
@@ -160,7 +162,12 @@ def enable_fused_fsdp(
     happened; ``.check()`` raises if a device-side wait timed out), or ``None`` when the
     data-parallel group has a single rank (FSDP2 then performs no reduce-scatter).
     ``depth`` symmetric buffers of the largest group's gradient size are kept.
+    ``max_ctas`` caps the kernel's grid: the reduce-scatter is NVLink-bound, so a few
+    dozen CTAs keep the links busy while the SMs stay with backward's GEMMs.
+    ``use_multicast`` fetches each unit with one ``multimem.ld_reduce`` (the NVSwitch
+    adds the ranks' copies and returns the sum narrowed to the gradient dtype, 1/world
+    of the inbound traffic of peer loads) instead of ``world`` peer loads summed in fp32.
     """
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return None
-    return FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth)
+    return FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas)

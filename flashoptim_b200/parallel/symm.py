@@ -66,6 +66,7 @@ class PeerGroup:
         device: Optional[torch.device] = None,
         timeout_s: float = 2.0,
         use_multicast: bool = True,
+        max_ctas: int = 0,
     ):
         self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
         self.world = dist.get_world_size(self.group) if self.group is not None else 1
@@ -75,6 +76,7 @@ class PeerGroup:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.timeout_ns = int(timeout_s * 1e9)
         self.use_multicast = use_multicast
+        self.max_ctas = max_ctas  # grid cap of the peer kernels (0: fill the GPU)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._pad = self.allocate(CHANNELS * native.FO_MAX_PEERS * 4, zero=True)
         self._next_channel = 0
@@ -142,6 +144,7 @@ class PeerGroup:
         a.rank = rank if rank is not None else self.rank
         a.ready_channel = ready_channel
         a.done_channel = done_channel
+        a.max_ctas = self.max_ctas
         return a
 
     # ------------------------------------------------------------------ flags

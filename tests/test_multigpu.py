@@ -62,8 +62,6 @@ def _peer_kernel_worker(rank, world, use_multicast):
     # NCCL reference for the mean gradient
     gsum = buf.view(0, n, torch.bfloat16).float()
     dist.all_reduce(gsum)
-    if use_multicast:
-        gsum = gsum.to(torch.bfloat16).float()  # the switch hands back its fp32 sum rounded to bf16
     gmean = (gsum / world).cpu()
     p_old = oracle.ecc_decode_ref(p.cpu(), ecc.cpu())
     want_p, want_m, want_v = oracle.adam_math(
@@ -82,11 +80,19 @@ def _peer_kernel_worker(rank, world, use_multicast):
     peers.check_status()
     rec = oracle.ecc_decode_ref(p.cpu(), ecc.cpu())
     half_ulp = torch.exp2(oracle.ecc_log_scale(p.cpu()).float())
-    g_tol = 0
-    bad = (rec - want_p).abs() > half_ulp * 0.75 / 127 + 4e-6 * (want_p - p_old).abs() + 4e-7 * want_p.abs() + 1e-10 + g_tol
+    # multimem.ld_reduce hands back the switch's fp32 sum narrowed to bf16 (observed: up to one
+    # bf16 ULP away from the exact sum); propagate that gradient error through the step:
+    # d(update) = lr * dg / (sqrt(v_hat) + eps) at step 1
+    g_tol = (1e-3 * 1.5 * 2 ** -7 * gmean.abs() / ((want_v / (1 - 0.999)).sqrt() + 1e-8)) if use_multicast else 0
+    bound = half_ulp * 0.75 / 127 + 4e-6 * (want_p - p_old).abs() + 4e-7 * want_p.abs() + 1e-10 + g_tol
+    diff = (rec - want_p).abs()
+    bad = diff > bound
     if bad.any():
-        errors.append(f"rank {rank} mc={use_multicast}: {int(bad.sum())} params off")
-    if not torch.allclose(out.float().cpu(), gmean, rtol=2 ** -6, atol=1e-8):
+        i = int((diff / bound).argmax())
+        errors.append(f"rank {rank} mc={use_multicast}: {int(bad.sum())} params off, worst x{float((diff / bound).max()):.1f} "
+                      f"at {i}: got {float(rec[i])} want {float(want_p[i])} old {float(p_old[i])} g {float(gmean[i])} "
+                      f"handed-back g {float(out[i])}")
+    if not torch.allclose(out.float().cpu(), gmean, rtol=2 ** -6 if use_multicast else 2 ** -7, atol=1e-8):
         errors.append(f"rank {rank} mc={use_multicast}: averaged gradient hand-back is off")
     # replicas bit-identical
     for t in (p, ecc, m, v):
