@@ -75,11 +75,16 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=32, help="fewer layers = smaller problem (profiling)")
     ap.add_argument("--vocab", type=int, default=128256, help="smaller vocabulary = smaller problem")
+    ap.add_argument("--variant", type=int, default=None, help="ours: 0 register-path kernels, 1 staged (default)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    if args.variant is not None and args.impl == "ours":
+        from flashoptim_b200.ops.step import set_step_variant
+
+        set_step_variant(args.variant)
     peak, peak_src = hbm_peak_gbs()
     shapes = llama8b_shapes(layers=args.layers, vocab=args.vocab)
     g = torch.Generator(device=dev).manual_seed(0)

@@ -70,6 +70,15 @@ int fo_chunk_elems(void);
 // Number of CTAs the step kernels are launched with on `device` (<= total chunks).
 int fo_step_grid(int device);
 
+// Kernel family of the fused steps: 1 (default) streams bf16/fp16 tensors with 8-bit
+// states through shared memory with cp.async.bulk + mbarrier stages, 0 always uses the
+// register-path kernels (which also serve every other combination).
+void fo_set_step_variant(int variant);
+int fo_get_step_variant(void);
+// Optional: a zeroed device uint32 (of the current device) in which a kernel sets a bit
+// when one of its bounded waits ran out (1: producer, 2: consumer of the staged kernels).
+int fo_set_step_status(void* device_word);
+
 // Multi-tensor fused steps.  `segs` / `chunk_begin` are HOST pointers when
 // n_seg <= FO_MAX_INLINE_SEGS and `table_on_device` is 0 (the table then
 // travels in the kernel parameters, no device memory is touched), DEVICE

@@ -9,69 +9,9 @@
 // moments are read once, the update runs in fp32 registers, and parameter,
 // correction and requantised moments are written once
 // (what flashoptim/optimizers.py:2255-2438 and :1586-1719 compute).
-#include "fo_step_core.cuh"
+#include "fo_step_table.cuh"
 
 namespace fo {
-
-#ifndef FO_UNROLL
-#define FO_UNROLL 1
-#endif
-#ifndef FO_CTAS_PER_SM
-#define FO_CTAS_PER_SM 4
-#endif
-#ifndef FO_THREADS
-#define FO_THREADS 256
-#endif
-constexpr int kThreads = FO_THREADS;
-constexpr int kUnroll = FO_UNROLL;  // units per thread per chunk; all loads of a chunk are issued before any math
-constexpr int kChunk = kThreads * kUnit * kUnroll;
-constexpr int kCtasPerSm = FO_CTAS_PER_SM;
-
-struct InlineTable {
-  FoSeg segs[FO_MAX_INLINE_SEGS];
-  int32_t chunk_begin[FO_MAX_INLINE_SEGS + 1];
-};
-
-struct StepParams {
-  const FoSeg* segs;           // device table (null when inline)
-  const int32_t* chunk_begin;  // device table (null when inline)
-  int n_seg;
-  int total_chunks;
-  InlineTable inl;
-};
-
-// Walks the chunk list of one CTA: chunk c belongs to the segment s with
-// chunk_begin[s] <= c < chunk_begin[s + 1]; a CTA visits chunks in increasing
-// order, so the segment index only ever moves forward.
-struct ChunkWalker {
-  const FoSeg* segs;
-  const int32_t* cb;
-  int total;
-  int seg, seg_begin, seg_end;
-  FoSeg S;
-  bool vec;
-
-  __device__ __forceinline__ ChunkWalker(const StepParams& P)
-      : segs(P.segs ? P.segs : P.inl.segs), cb(P.chunk_begin ? P.chunk_begin : P.inl.chunk_begin),
-        total(P.total_chunks), seg(0) {
-    seg_begin = cb[0];
-    seg_end = cb[1];
-    S = segs[0];
-    vec = seg_vector_safe(S);
-  }
-  __device__ __forceinline__ void seek(int c) {
-    if (c >= seg_end) {
-      do { ++seg; } while (c >= cb[seg + 1]);
-      S = segs[seg];
-      seg_begin = cb[seg];
-      seg_end = cb[seg + 1];
-      vec = seg_vector_safe(S);
-    }
-  }
-  __device__ __forceinline__ int64_t unit_base(int c, int u) const {
-    return (int64_t)(c - seg_begin) * kChunk + (int64_t)(u * kThreads + threadIdx.x) * kUnit;
-  }
-};
 
 // Occupancy (4 CTAs of 256 threads at 64 registers), not register-level software
 // prefetch, hides the memory latency here: a double-buffered variant of this loop
@@ -160,10 +100,17 @@ static int sm_count(int device) {
   return g_sm_count[device];
 }
 
+// 0: register-path kernels only; 1: bulk-copy staged kernels where they apply
+static int g_step_variant = 1;
+static unsigned int* g_status[64];
+
 static int fill_params(StepParams& P, const FoSeg* segs, const int32_t* chunk_begin, int n_seg,
                        int total_chunks, int table_on_device) {
   P.n_seg = n_seg;
   P.total_chunks = total_chunks;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  P.status = (dev >= 0 && dev < 64) ? g_status[dev] : nullptr;
   if (table_on_device) {
     P.segs = segs;
     P.chunk_begin = chunk_begin;
@@ -227,6 +174,15 @@ static int grid_for(int total_chunks) {
 
 extern "C" int fo_chunk_elems(void) { return fo::kChunk; }
 
+extern "C" void fo_set_step_variant(int variant) { fo::g_step_variant = variant; }
+extern "C" int fo_get_step_variant(void) { return fo::g_step_variant; }
+extern "C" int fo_set_step_status(void* device_word) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  fo::g_status[dev] = static_cast<unsigned int*>(device_word);
+  return 0;
+}
+
 extern "C" int fo_step_grid(int device) { return fo::sm_count(device) * fo::kCtasPerSm; }
 
 extern "C" int fo_adam_step(const FoSeg* segs, const int32_t* chunk_begin, int n_seg, int total_chunks,
@@ -238,6 +194,12 @@ extern "C" int fo_adam_step(const FoSeg* segs, const int32_t* chunk_begin, int n
   if (rc) return rc;
   const int grid = fo::grid_for(total_chunks);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (fo::g_step_variant == 1) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    rc = fo::staged_adam_launch(P, *hyper, dtype, err_bytes, quantized, fo::sm_count(dev), st);
+    if (rc != -1) return rc;
+  }
   switch (dtype) {
     case FO_BF16: return fo::launch_adam_e<__nv_bfloat16>(P, *hyper, err_bytes, quantized, grid, st);
     case FO_FP16: return fo::launch_adam_e<__half>(P, *hyper, err_bytes, quantized, grid, st);
@@ -255,6 +217,12 @@ extern "C" int fo_momentum_step(const FoSeg* segs, const int32_t* chunk_begin, i
   if (rc) return rc;
   const int grid = fo::grid_for(total_chunks);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (fo::g_step_variant == 1) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    rc = fo::staged_momentum_launch(P, *hyper, dtype, err_bytes, state_mode, fo::sm_count(dev), st);
+    if (rc != -1) return rc;
+  }
   switch (dtype) {
     case FO_BF16: return fo::launch_mom_e<__nv_bfloat16>(P, *hyper, err_bytes, state_mode, grid, st);
     case FO_FP16: return fo::launch_mom_e<__half>(P, *hyper, err_bytes, state_mode, grid, st);

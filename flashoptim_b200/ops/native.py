@@ -103,6 +103,12 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.fo_chunk_elems.argtypes = []
     lib.fo_step_grid.restype = c_int
     lib.fo_step_grid.argtypes = [c_int]
+    lib.fo_set_step_variant.restype = None
+    lib.fo_set_step_variant.argtypes = [c_int]
+    lib.fo_get_step_variant.restype = c_int
+    lib.fo_get_step_variant.argtypes = []
+    lib.fo_set_step_status.restype = c_int
+    lib.fo_set_step_status.argtypes = [c_void_p]
     lib.fo_adam_step.restype = c_int
     lib.fo_adam_step.argtypes = [
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(FoAdamHyper), c_void_p,

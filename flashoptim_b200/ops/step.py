@@ -32,6 +32,39 @@ def launch_count() -> int:
     return _launches
 
 
+class StepKernelError(RuntimeError):
+    """A bounded wait inside a step kernel ran out (the update of that launch is incomplete)."""
+
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def _ensure_status(device: torch.device) -> None:
+    """Give the kernels of ``device`` a word to report a wait that ran out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        with torch.cuda.device(idx):
+            native.check(native.load().fo_set_step_status(t.data_ptr()), "fo_set_step_status")
+        _status[idx] = t
+
+
+def check_kernel_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise :class:`StepKernelError` if a step kernel reported a timeout."""
+    for idx, t in list(_status.items()):
+        if device is not None and device.index not in (None, idx):
+            continue
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise StepKernelError(f"cuda:{idx}: step kernel wait timed out (code {code})")
+
+
+def set_step_variant(variant: int) -> None:
+    """0: register-path kernels only; 1 (default): bulk-copy staged kernels where they apply."""
+    native.load().fo_set_step_variant(int(variant))
+
+
 
 @dataclass
 class AdamHyper:
@@ -141,6 +174,7 @@ def launch_adam(
     if rows.shape[0] == 0:
         return
     lib = native.load()
+    _ensure_status(table.device)
     segs, chunks, n_seg, total, on_dev = table.prepare(rows)
     h = hyper.to_c()
     with torch.cuda.device(table.device):
@@ -165,6 +199,7 @@ def launch_momentum(
     if rows.shape[0] == 0:
         return
     lib = native.load()
+    _ensure_status(table.device)
     segs, chunks, n_seg, total, on_dev = table.prepare(rows)
     h = hyper.to_c()
     with torch.cuda.device(table.device):

@@ -14,6 +14,17 @@ from flashoptim_b200.ops.step import (
 
 pytestmark = pytest.mark.gpu
 
+
+@pytest.fixture(params=["staged", "register"], autouse=True)
+def step_variant(request):
+    """Every test runs with the bulk-copy staged kernels (default) and with the register-path kernels."""
+    from flashoptim_b200.ops.step import check_kernel_status, set_step_variant
+
+    set_step_variant(1 if request.param == "staged" else 0)
+    yield request.param
+    set_step_variant(1)
+    check_kernel_status()
+
 SIZES = [1, 5, 31, 32, 33, 999, 1025, 4097, 2048 * 8 + 3, 1 << 20]
 DTYPES = [torch.bfloat16, torch.float16, torch.float32]
 
