@@ -20,11 +20,22 @@
 
 namespace fo {
 
-constexpr int kStages = 4;
+// Ring depth and CTAs per SM.  On the 291-tensor Llama-3-8B list 4 stages x 3 CTAs
+// (9 chunks = 131 KB in flight per SM) measured best or within noise of the best for
+// every kernel; deeper rings with 2 CTAs win on a single huge tensor but not on the
+// list.  -DFO_STAGES / -DFO_STAGED_CTAS_PER_SM override both for tuning builds.
+template <int kErr>
+struct StageConfig {
+#if defined(FO_STAGES) && defined(FO_STAGED_CTAS_PER_SM)
+  static constexpr int kStages = FO_STAGES, kCtasPerSm = FO_STAGED_CTAS_PER_SM;
+#else
+  static constexpr int kStages = 4;
+  static constexpr int kCtasPerSm = 3;
+#endif
+};
 constexpr int kConsumerThreads = 256;
 constexpr int kConsumerWarps = kConsumerThreads / 32;
 constexpr int kStagedThreads = kConsumerThreads + 32;
-constexpr int kStagedCtasPerSm = 3;
 constexpr int kStagedChunk = kConsumerThreads * kUnit;  // must equal kChunk of the table
 static_assert(kStagedChunk == kChunk, "staged kernels share the chunk prefix of the register path");
 constexpr uint64_t kStageWaitNs = 2000000000ull;
@@ -99,6 +110,7 @@ template <typename T, int kErr, int kStates, typename Hyper, typename Update>
 __device__ __forceinline__ void staged_body(const StepParams& P, const Hyper& H, Update update) {
   using L = StageLayout<kErr, kStates>;
   using Regs = UnitRegs<T, kErr, kStates, true>;
+  constexpr int kStages = StageConfig<kErr>::kStages;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kStages], empty[kStages];
 
@@ -209,22 +221,22 @@ struct MomentumUpdate {
 };
 
 template <typename T, int kErr>
-__global__ void __launch_bounds__(kStagedThreads, kStagedCtasPerSm)
+__global__ void __launch_bounds__(kStagedThreads, StageConfig<kErr>::kCtasPerSm)
     adam_staged_kernel(const __grid_constant__ StepParams P, const __grid_constant__ FoAdamHyper H) {
   staged_body<T, kErr, 2>(P, H, AdamUpdate());
 }
 template <typename T, int kErr>
-__global__ void __launch_bounds__(kStagedThreads, kStagedCtasPerSm)
+__global__ void __launch_bounds__(kStagedThreads, StageConfig<kErr>::kCtasPerSm)
     momentum_staged_kernel(const __grid_constant__ StepParams P, const __grid_constant__ FoMomentumHyper H) {
   staged_body<T, kErr, 1>(P, H, MomentumUpdate());
 }
 
-template <typename Kernel, typename Hyper>
-static int launch_staged(Kernel kernel, int smem_bytes, const StepParams& P, const Hyper& H, int sm_count,
-                         cudaStream_t st) {
+template <int kErr, int kStates, typename Kernel, typename Hyper>
+static int launch_staged(Kernel kernel, const StepParams& P, const Hyper& H, int sm_count, cudaStream_t st) {
+  constexpr int smem_bytes = StageConfig<kErr>::kStages * StageLayout<kErr, kStates>::kStride;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return (int)e;
-  int grid = sm_count * kStagedCtasPerSm;
+  int grid = sm_count * StageConfig<kErr>::kCtasPerSm;
   if (P.total_chunks < grid) grid = P.total_chunks;
   kernel<<<grid, kStagedThreads, smem_bytes, st>>>(P, H);
   return (int)cudaGetLastError();
@@ -233,18 +245,18 @@ static int launch_staged(Kernel kernel, int smem_bytes, const StepParams& P, con
 template <typename T>
 static int staged_adam_t(const StepParams& P, const FoAdamHyper& H, int err, int sms, cudaStream_t st) {
   switch (err) {
-    case 0: return launch_staged(adam_staged_kernel<T, 0>, kStages * StageLayout<0, 2>::kStride, P, H, sms, st);
-    case 1: return launch_staged(adam_staged_kernel<T, 1>, kStages * StageLayout<1, 2>::kStride, P, H, sms, st);
-    case 2: return launch_staged(adam_staged_kernel<T, 2>, kStages * StageLayout<2, 2>::kStride, P, H, sms, st);
+    case 0: return launch_staged<0, 2>(adam_staged_kernel<T, 0>, P, H, sms, st);
+    case 1: return launch_staged<1, 2>(adam_staged_kernel<T, 1>, P, H, sms, st);
+    case 2: return launch_staged<2, 2>(adam_staged_kernel<T, 2>, P, H, sms, st);
   }
   return -1;
 }
 template <typename T>
 static int staged_momentum_t(const StepParams& P, const FoMomentumHyper& H, int err, int sms, cudaStream_t st) {
   switch (err) {
-    case 0: return launch_staged(momentum_staged_kernel<T, 0>, kStages * StageLayout<0, 1>::kStride, P, H, sms, st);
-    case 1: return launch_staged(momentum_staged_kernel<T, 1>, kStages * StageLayout<1, 1>::kStride, P, H, sms, st);
-    case 2: return launch_staged(momentum_staged_kernel<T, 2>, kStages * StageLayout<2, 1>::kStride, P, H, sms, st);
+    case 0: return launch_staged<0, 1>(momentum_staged_kernel<T, 0>, P, H, sms, st);
+    case 1: return launch_staged<1, 1>(momentum_staged_kernel<T, 1>, P, H, sms, st);
+    case 2: return launch_staged<2, 1>(momentum_staged_kernel<T, 2>, P, H, sms, st);
   }
   return -1;
 }
