@@ -45,6 +45,11 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--master-weight-bits", default="24")
+    ap.add_argument("--optimizer", default="adamw", choices=["adamw", "lion"])
+    ap.add_argument("--compress-state-dict", action="store_true")
+    ap.add_argument("--dcp-dir", default=None,
+                    help="after the timed loops, time a torch.distributed.checkpoint save + load of the "
+                         "sharded optimizer state into this directory")
     ap.add_argument("--gradient-release", action="store_true")
     ap.add_argument("--activation-checkpointing", action="store_true")
     ap.add_argument("--fused-comm", default="auto", choices=["auto", "off"],
@@ -165,13 +170,14 @@ def main():
     cfg.max_seq_len = args.seq_len
     cfg.activation_checkpointing = args.activation_checkpointing or args.model == "llama3-70b"
 
-    torch.manual_seed(0)
+    # Build on the meta device, shard, then materialise and initialise only the local
+    # shards: a 70 B model never exists unsharded on one GPU.
+    torch.manual_seed(1234 + rank)
     prev = torch.get_default_dtype()
-    torch.set_default_dtype(torch.bfloat16)  # build directly in bf16: no 32 GB fp32 transient
-    with torch.device(dev):
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device("meta"):
         model = llama.Llama(cfg)
     torch.set_default_dtype(prev)
-    model.init_weights(0.02, seed=0)
     lib.cast_model(model, dtype=torch.bfloat16)
     n_params = sum(p.numel() for p in model.parameters())
 
@@ -180,13 +186,25 @@ def main():
     for layer in model.layers:
         fully_shard(layer)
     fully_shard(model)
+    model.to_empty(device=dev)
+    with torch.no_grad():
+        for p in model.parameters():
+            local = p._local_tensor if hasattr(p, "_local_tensor") else p
+            if p.dim() >= 2:
+                local.normal_(0.0, 0.02)
+            else:
+                local.fill_(1.0)
 
     mwb = None if args.master_weight_bits.lower() == "none" else int(args.master_weight_bits)
     import warnings
 
     warnings.simplefilter("ignore")
-    opt = lib.FlashAdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.01,
-                         master_weight_bits=mwb)
+    if args.optimizer == "lion":
+        opt = lib.FlashLion(model.parameters(), lr=1e-5, betas=(0.9, 0.99), weight_decay=0.01,
+                            master_weight_bits=mwb, compress_state_dict=args.compress_state_dict)
+    else:
+        opt = lib.FlashAdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.01,
+                             master_weight_bits=mwb, compress_state_dict=args.compress_state_dict)
     fused_comm = False
     if args.impl == "ours" and args.fused_comm == "auto":
         try:
@@ -258,6 +276,35 @@ def main():
     sampler.stop()
     dist.barrier()
 
+    dcp_times = None
+    if args.dcp_dir:
+        import shutil
+
+        import torch.distributed.checkpoint as dcp
+        from torch.distributed.checkpoint.state_dict import get_optimizer_state_dict, set_optimizer_state_dict
+
+        torch.cuda.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        osd = get_optimizer_state_dict(model, opt)
+        dcp.save({"optimizer": osd}, checkpoint_id=args.dcp_dir)
+        torch.cuda.synchronize()
+        dist.barrier()
+        t1 = time.perf_counter()
+        template = get_optimizer_state_dict(model, opt)
+        dcp.load({"optimizer": template}, checkpoint_id=args.dcp_dir)
+        set_optimizer_state_dict(model, opt, template)
+        torch.cuda.synchronize()
+        dist.barrier()
+        t2 = time.perf_counter()
+        size = 0
+        if rank == 0:
+            for root, _, files in os.walk(args.dcp_dir):
+                size += sum(os.path.getsize(os.path.join(root, f)) for f in files)
+            shutil.rmtree(args.dcp_dir, ignore_errors=True)
+        dcp_times = {"save_s": round(t1 - t0, 3), "load_s": round(t2 - t1, 3), "bytes_on_disk": size,
+                     "compressed": bool(args.compress_state_dict)}
+
     t = torch.tensor([dev_ms, e2e_ms, torch.cuda.max_memory_allocated() / 2**30], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms, peak_gib = (float(x) for x in t.tolist())
@@ -279,7 +326,8 @@ def main():
             "data": "synthetic uniform token ids, random-init weights N(0,0.02)",
             "config": {
                 "model": args.model, "n_params": n_params, "global_batch": world * b, "seq_len": s,
-                "parallelism": f"fsdp2x{world}", "optimizer": f"FlashAdamW mwb={mwb}",
+                "parallelism": f"fsdp2x{world}",
+                "optimizer": f"{'FlashLion' if args.optimizer == 'lion' else 'FlashAdamW'} mwb={mwb}",
                 "gradient_release": bool(args.gradient_release), "fused_comm": bool(fused_comm),
                 "fused_comm_multicast": bool(fused_comm and not args.no_multicast),
                 "activation_checkpointing": bool(cfg.activation_checkpointing),
@@ -297,6 +345,8 @@ def main():
             "peak_gib_per_gpu": round(peak_gib, 2),
             "clocks": sampler.summary(),
         }
+        if dcp_times is not None:
+            rec["dcp"] = dcp_times
         print(json.dumps(rec), flush=True)
     dist.destroy_process_group()
 

@@ -94,7 +94,9 @@ def cast_model(
     converted: dict[int, torch.Tensor] = {}  # storage address -> cast tensor (keeps ties)
 
     def convert(t: torch.Tensor) -> torch.Tensor:
-        key = t.data.data_ptr()
+        # tensors without storage (meta device) all report address 0: key those by identity,
+        # which still keeps parameters tied through one Parameter object tied
+        key = t.data.data_ptr() if t.device.type != "meta" else -id(t)
         if key not in converted:
             converted[key] = t.data.to(dtype=dtype)
         return converted[key]

@@ -115,3 +115,11 @@ def test_tuple_outputs_are_recast():
     cast_model(m, full_precision_recast_layers=["two"])
     a, k, b = m(torch.randn(2, 4).bfloat16())
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and k == 3
+
+
+def test_meta_device_parameters_are_not_merged():
+    with torch.device("meta"):
+        m = nn.Sequential(nn.Linear(4, 8), nn.Linear(8, 2))
+    cast_model(m)
+    assert m[0].weight.shape == (8, 4) and m[1].weight.shape == (2, 8)
+    assert m[0].weight.dtype == torch.bfloat16 and m[0].weight.device.type == "meta"
