@@ -112,7 +112,8 @@ def test_kernels_agree_with_reference_kernels():
         q2, s2 = ours.quantize(xi, signed=signed, sqrt=sqrt, softsign=softsign)
         d = (q1.to(torch.int16) - q2.to(torch.int16)).abs()
         assert d.max() <= 1 and (d != 0).float().mean() < 5e-3  # Triton's approximate division flips rare ties
-        assert torch.equal(s1, s2)
+        # Triton's approximate sqrt can move a scale by one fp16 ULP
+        assert torch.allclose(s1.float(), s2.float(), rtol=2e-3, atol=0)
         a = ref_dequantize(q2, s2, signed=signed, sqrt=sqrt, softsign=softsign)
         b = ours.dequantize(q2, s2, signed=signed, sqrt=sqrt, softsign=softsign)
         assert torch.allclose(a, b, rtol=1e-5, atol=1e-12)
