@@ -170,30 +170,41 @@ def main():
     cfg.max_seq_len = args.seq_len
     cfg.activation_checkpointing = args.activation_checkpointing or args.model == "llama3-70b"
 
-    # Build on the meta device, shard, then materialise and initialise only the local
-    # shards: a 70 B model never exists unsharded on one GPU.
-    torch.manual_seed(1234 + rank)
-    prev = torch.get_default_dtype()
-    torch.set_default_dtype(torch.bfloat16)
-    with torch.device("meta"):
-        model = llama.Llama(cfg)
-    torch.set_default_dtype(prev)
-    lib.cast_model(model, dtype=torch.bfloat16)
-    n_params = sum(p.numel() for p in model.parameters())
-
     from torch.distributed.fsdp import fully_shard
 
-    for layer in model.layers:
-        fully_shard(layer)
-    fully_shard(model)
-    model.to_empty(device=dev)
-    with torch.no_grad():
-        for p in model.parameters():
-            local = p._local_tensor if hasattr(p, "_local_tensor") else p
-            if p.dim() >= 2:
-                local.normal_(0.0, 0.02)
-            else:
-                local.fill_(1.0)
+    torch.manual_seed(1234 + rank)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)  # construct in bf16: no fp32 transient
+    if args.model == "llama3-70b":
+        # Too large to exist unsharded on one GPU: build on the meta device, shard, then
+        # materialise and initialise only the local shards.  Parameters are already bf16,
+        # so cast_model is not called here (on storage-less meta tensors the reference's
+        # cast_model keys every tensor by address 0 and would merge them).
+        with torch.device("meta"):
+            model = llama.Llama(cfg)
+        torch.set_default_dtype(prev)
+        n_params = sum(p.numel() for p in model.parameters())
+        for layer in model.layers:
+            fully_shard(layer)
+        fully_shard(model)
+        model.to_empty(device=dev)
+        with torch.no_grad():
+            for p in model.parameters():
+                local = p._local_tensor if hasattr(p, "_local_tensor") else p
+                if p.dim() >= 2:
+                    local.normal_(0.0, 0.02)
+                else:
+                    local.fill_(1.0)
+    else:
+        with torch.device(dev):
+            model = llama.Llama(cfg)
+        torch.set_default_dtype(prev)
+        model.init_weights(0.02, seed=0)
+        lib.cast_model(model, dtype=torch.bfloat16)
+        n_params = sum(p.numel() for p in model.parameters())
+        for layer in model.layers:
+            fully_shard(layer)
+        fully_shard(model)
 
     mwb = None if args.master_weight_bits.lower() == "none" else int(args.master_weight_bits)
     import warnings
