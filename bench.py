@@ -55,6 +55,8 @@ def parse_args():
     ap.add_argument("--fused-comm", default="auto", choices=["auto", "off"],
                     help="ours only: fuse the FSDP2 collectives with the update where supported")
     ap.add_argument("--comm-ctas", type=int, default=0, help="grid cap of the fused reduce-scatter kernel")
+    ap.add_argument("--own-all-gather", action="store_true",
+                    help="fused path: FSDP2's parameter all-gather through this library's pull kernel")
     ap.add_argument("--no-multicast", action="store_true",
                     help="fused path: sum peer loads in fp32 instead of NVSwitch multimem.ld_reduce")
     return ap.parse_args()
@@ -221,7 +223,8 @@ def main():
         try:
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
-            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, max_ctas=args.comm_ctas, use_multicast=not args.no_multicast)
+            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, max_ctas=args.comm_ctas, use_multicast=not args.no_multicast,
+                                                         own_all_gather=args.own_all_gather)
             fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
             if rank == 0:

@@ -36,6 +36,8 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--comm-ctas", type=int, default=0, help="fused: grid cap of the all-reduce + update kernel")
+    ap.add_argument("--multicast", action="store_true", help="fused: NVSwitch multimem.ld_reduce")
     args = ap.parse_args()
     if args.mode == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
@@ -76,7 +78,7 @@ def main():
     if args.mode == "fused":
         from flashoptim_b200.parallel import fuse_ddp_allreduce
 
-        state = fuse_ddp_allreduce(ddp, opt)
+        state = fuse_ddp_allreduce(ddp, opt, use_multicast=args.multicast, max_ctas=args.comm_ctas)
 
     b, s = args.micro_batch, args.seq_len
     g = torch.Generator().manual_seed(99 + rank)

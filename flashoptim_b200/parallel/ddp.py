@@ -40,6 +40,7 @@ class FusedDDPState:
         timeout_s: float = 5.0,
         use_multicast: bool = False,
         write_back: bool = False,
+        max_ctas: int = 0,
     ):
         params = [p for p in ddp_model.parameters() if p.requires_grad]
         if not params:
@@ -48,7 +49,8 @@ class FusedDDPState:
             raise ValueError("the fused DDP path needs CUDA parameters")
         self.optimizer = optimizer
         self.write_back = write_back
-        self.peers = PeerGroup(group, device=params[0].device, timeout_s=timeout_s, use_multicast=use_multicast)
+        self.peers = PeerGroup(group, device=params[0].device, timeout_s=timeout_s, use_multicast=use_multicast,
+                               max_ctas=max_ctas)
         # every bucket gets a 256-byte aligned slice; one slice per parameter is the worst case
         total = sum(p.numel() * p.element_size() for p in params) + 256 * (len(params) + 1)
         self.arena = self.peers.allocate(total)
@@ -106,6 +108,7 @@ def fuse_ddp_allreduce(
     timeout_s: float = 5.0,
     use_multicast: bool = False,
     write_back: bool = False,
+    max_ctas: int = 0,
 ) -> FusedDDPState:
     """Fuse DDP's per-bucket gradient all-reduce with ``optimizer``'s update.
 
@@ -119,6 +122,6 @@ def fuse_ddp_allreduce(
     """
     if not isinstance(ddp_model, DDP):
         raise TypeError("fuse_ddp_allreduce expects a DistributedDataParallel model")
-    state = FusedDDPState(ddp_model, optimizer, group, timeout_s, use_multicast, write_back)
+    state = FusedDDPState(ddp_model, optimizer, group, timeout_s, use_multicast, write_back, max_ctas)
     ddp_model.register_comm_hook(state, state.hook)
     return state

@@ -30,12 +30,17 @@ import torch.nn as nn
 from ..optim.base import FlashOptimizer, local_tensor
 from .symm import PeerGradients, PeerGroup
 
+import ctypes
+
+from ..ops import native
+
 try:  # torch >= 2.8
     from torch.distributed.fsdp import FSDPModule
-    from torch.distributed.fsdp._fully_shard._fsdp_api import ReduceScatter
+    from torch.distributed.fsdp._fully_shard._fsdp_api import AllGather, ReduceScatter
 except Exception:  # pragma: no cover
     FSDPModule = None  # type: ignore[assignment]
     ReduceScatter = object  # type: ignore[assignment,misc]
+    AllGather = object  # type: ignore[assignment,misc]
 
 
 class _Pool:
@@ -111,9 +116,50 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
         return None
 
 
+class PeerAllGather(AllGather):  # type: ignore[misc,valid-type]
+    """FSDP2's parameter all-gather done by this library's pull kernel.
+
+    FSDP2 allocates the ``[world, shard]`` all-gather output through :meth:`allocate`
+    (here: a symmetric buffer from a small pool), copies its own shards into slot
+    ``rank`` and calls the communicator; every rank then pulls slot ``s`` from rank
+    ``s`` over NVLink with plain 16-byte peer loads (``fo_allgather_peer``).  Calls whose
+    slot size is not a multiple of 16 bytes, or that are larger than the pool's buffers,
+    use NCCL.
+    """
+
+    def __init__(self, ctx: "FusedFSDPState") -> None:
+        self.ctx = ctx
+        self._slot: Optional[PeerGradients] = None
+
+    def allocate(self, size, *, dtype, device):
+        numel = int(size[0])
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        w = self.ctx.peers.world
+        if nbytes <= self.ctx.ag_pool_bytes and (nbytes // w) % 16 == 0 and nbytes % w == 0:
+            slot = self.ctx.ag_pool.take()
+            slot.wait_done()  # peers have pulled my slot's previous contents
+            self._slot = slot
+            return slot.buf.view(0, numel, dtype)
+        self._slot = None
+        return torch.empty(*size, dtype=dtype, device=device)
+
+    def __call__(self, output_tensor, input_tensor, group, async_op=False):
+        slot, self._slot = self._slot, None
+        if slot is None or output_tensor.data_ptr() != slot.buf.tensor.data_ptr() or async_op:
+            self.ctx.ag_fallbacks += 1
+            return dist.all_gather_into_tensor(output_tensor, input_tensor, group=group, async_op=async_op)
+        slot_bytes = input_tensor.numel() * input_tensor.element_size()
+        args = slot.next_args()
+        rc = native.load().fo_allgather_peer(slot_bytes, ctypes.byref(args),
+                                             native.stream_ptr(self.ctx.peers.device))
+        native.check(rc, "fo_allgather_peer")
+        self.ctx.ag_calls += 1
+        return None
+
+
 class FusedFSDPState:
     def __init__(self, model: nn.Module, optimizer: FlashOptimizer, group, timeout_s, use_multicast, depth,
-                 max_ctas=0):
+                 max_ctas=0, own_all_gather=False):
         self.optimizer = optimizer
         modules = [m for m in model.modules() if FSDPModule is not None and isinstance(m, FSDPModule)]
         if not modules:
@@ -140,6 +186,15 @@ class FusedFSDPState:
         self.pool = _Pool(self.peers, need, depth)
         for m, comm in self.comms:
             m.set_custom_reduce_scatter(comm)
+        self.ag_calls = 0
+        self.ag_fallbacks = 0
+        if own_all_gather:
+            # the all-gather output of a group is as large as its reduce-scatter input;
+            # three buffers: one being copied out, one prefetched, one spare
+            self.ag_pool_bytes = need
+            self.ag_pool = _Pool(self.peers, need, 3)
+            for m, _ in groups:
+                m.set_custom_all_gather(PeerAllGather(self))
 
     def check(self) -> None:
         self.peers.check_status()
@@ -154,6 +209,7 @@ def enable_fused_fsdp(
     use_multicast: bool = False,
     depth: int = 2,
     max_ctas: int = 0,
+    own_all_gather: bool = False,
 ) -> Optional[FusedFSDPState]:
     """Fuse FSDP2's gradient reduce-scatter with ``optimizer``'s sharded update.
 
@@ -167,7 +223,9 @@ def enable_fused_fsdp(
     ``use_multicast`` fetches each unit with one ``multimem.ld_reduce`` (the NVSwitch
     adds the ranks' copies and returns the sum narrowed to the gradient dtype, 1/world
     of the inbound traffic of peer loads) instead of ``world`` peer loads summed in fp32.
+    ``own_all_gather`` also replaces FSDP2's parameter all-gather by this library's
+    pull kernel over symmetric buffers (:class:`PeerAllGather`).
     """
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return None
-    return FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas)
+    return FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas, own_all_gather)

@@ -190,7 +190,8 @@ def _fsdp_worker(rank, world):
             plain, fused = shard(_net(dev)), shard(_net(dev))
             o1 = cls(plain.parameters(), **kw)
             o2 = cls(fused.parameters(), **kw)
-            state = enable_fused_fsdp(fused, o2)
+            own_ag = release  # half of the cases also use the library's all-gather kernel
+            state = enable_fused_fsdp(fused, o2, own_all_gather=own_ag)
             if release:
                 enable_gradient_release(plain, o1)
                 enable_gradient_release(fused, o2)
@@ -209,6 +210,8 @@ def _fsdp_worker(rank, world):
                                             f"{cls.__name__} release={release} step {step} {n1}")
             if state.fused_calls < 5 or state.fallbacks:
                 errors.append(f"{cls.__name__} release={release}: fused {state.fused_calls}, fallbacks {state.fallbacks}")
+            if own_ag and state.ag_calls < 5:
+                errors.append(f"{cls.__name__}: own all-gather ran {state.ag_calls} times, fell back {state.ag_fallbacks}")
     return errors
 
 
