@@ -225,6 +225,11 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
     def _pre_step(self, param_state: dict[str, Any]) -> None:
         """Called once per parameter right before it is updated."""
 
+    def _pre_step_many(self, param_states: list[dict[str, Any]]) -> None:
+        """Same for all parameters of one fused launch (override to batch the work)."""
+        for st in param_states:
+            self._pre_step(st)
+
     # ------------------------------------------------------------------ DTensor helpers
     @staticmethod
     def _get_local_tensor(tensor: torch.Tensor) -> torch.Tensor:
@@ -367,12 +372,12 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
                     )
                 if g_local.dtype != p_local.dtype:
                     g_local = g_local.to(p_local.dtype)
-                self._pre_step(state)
                 fused_items.append((p_local, g_local, state))
             else:
                 self._pre_step(state)
                 self._eager_step(p_local, g_local, state.get("error_bits"), state, group)
         if fused_items:
+            self._pre_step_many([it[2] for it in fused_items])
             self._fused_step(fused_items, group, group_index)
 
     @torch.no_grad()
@@ -430,11 +435,10 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
                     raise RuntimeError("steps fused with the collective need contiguous CUDA parameters")
                 if self._check_numerics:
                     self._check_param_numerics(p, group["lr"], group["master_bytewidth"])
-                state = self.state[p]
-                self._pre_step(state)
-                items.append((p_local, int(peer.offsets[id(p_local)]), state))
+                items.append((p_local, int(peer.offsets[id(p_local)]), self.state[p]))
                 self._peer_stepped.add(id(p))
             if items:
+                self._pre_step_many([it[2] for it in items])
                 self._fused_step(items, group, gi, peer=peer)
 
     def zero_grad(self, set_to_none: bool = True) -> None:
