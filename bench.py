@@ -219,11 +219,12 @@ def main():
         opt = lib.FlashAdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.01,
                              master_weight_bits=mwb, compress_state_dict=args.compress_state_dict)
     fused_comm = False
+    fused_state = None
     if args.impl == "ours" and args.fused_comm == "auto":
         try:
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
-            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, max_ctas=args.comm_ctas, use_multicast=not args.no_multicast,
+            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=60.0, max_ctas=args.comm_ctas, use_multicast=not args.no_multicast,
                                                          own_all_gather=args.own_all_gather)
             fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
@@ -257,6 +258,8 @@ def main():
         train_step(dev_tokens[i])
         i += 1
     torch.cuda.synchronize()
+    if fused_state is not None:
+        fused_state.check()  # raises if a device-side wait for another rank ran out
     torch.cuda.reset_peak_memory_stats()
     sampler = ClockSampler(local_rank)
 
@@ -288,6 +291,8 @@ def main():
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
     sampler.stop()
+    if fused_state is not None:
+        fused_state.check()
     dist.barrier()
 
     dcp_times = None

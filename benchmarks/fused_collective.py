@@ -1,0 +1,139 @@
+"""Reduce-scatter fused with the sharded AdamW update vs NCCL reduce-scatter + local step.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29531 benchmarks/fused_collective.py --gpus 8
+
+One FSDP2-style parameter group: ``--numel`` bf16 gradient elements per rank laid
+out ``[world, shard]`` in a symmetric buffer (default 218 103 808 = one Llama-3-8B
+layer).  Rank r reduces row r of every rank and updates its shard (AdamW, 24-bit
+master weights, 8-bit states).  Timed on the device with CUDA events, max over
+ranks; every iteration touches far more than the 126 MB L2.
+
+Roofline of the fused kernel = the slower of
+  * NVLink: bytes that must arrive from peers / 770 GB/s (measured peer-copy rate):
+    peer loads bring (world-1) rows of shard*2 bytes; multimem.ld_reduce brings one
+    reduced row (the switch adds), i.e. shard*2 bytes;
+  * HBM: shard * (12.25 + 2) bytes (update traffic + this rank's own row, read by the
+    switch or by the kernel) / measured copy bandwidth.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--numel", type=int, default=218103808)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+
+    import torch
+    import torch.distributed as dist
+
+    from flashoptim_b200.ops.quant import quantize
+    from flashoptim_b200.ops.step import (
+        AdamHyper, SegmentTable, launch_adam, launch_adam_peer, make_rows,
+    )
+    from flashoptim_b200.parallel.symm import PeerGradients, PeerGroup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29535")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    n = args.numel // (world * 2048) * (world * 2048)
+    shard = n // world
+    peers = PeerGroup(timeout_s=30.0, use_multicast=True)
+    buf = peers.allocate(n * 2)
+    ready, done = peers.new_channels()
+    grads = buf.view(0, n, torch.bfloat16)
+    grads.normal_(0, 1e-3)
+    p = torch.empty(shard, dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
+    ecc = torch.zeros(shard, dtype=torch.int8, device=dev)
+    m, ms = quantize(torch.zeros(shard, device=dev))
+    v, vs = quantize(torch.zeros(shard, device=dev), signed=False, sqrt=True, softsign=False)
+    rs_out = torch.empty(shard, dtype=torch.bfloat16, device=dev)
+    table_peer, table_local = SegmentTable(dev), SegmentTable(dev)
+    rows_peer = make_rows([p], [None], [ecc], [m], [ms], [v], [vs])
+    rows_peer[:, 1] = rank * shard * 2
+    rows_local = make_rows([p], [rs_out], [ecc], [m], [ms], [v], [vs])
+
+    def hyper(step, scale):
+        return AdamHyper(lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=1e-6, step=step,
+                         decoupled=True, grad_scale=scale)
+
+    results = {}
+    for name in ("fused_peer_loads", "fused_multimem", "nccl_then_step"):
+        use_mc = name == "fused_multimem"
+        if use_mc and not buf.multicast_ptr:
+            continue
+        pg = PeerGradients(peers, buf, ready, done, grad_scale=1.0 / world)
+        peers.use_multicast = use_mc
+        pg.epoch = results.get("_epoch", 0)
+        step = [0]
+
+        def run():
+            step[0] += 1
+            if name == "nccl_then_step":
+                dist.reduce_scatter_tensor(rs_out, grads, op=dist.ReduceOp.AVG)
+                launch_adam(table_local, rows_local, torch.bfloat16, 1, True, hyper(step[0], 1.0))
+            else:
+                launch_adam_peer(table_peer, rows_peer, torch.bfloat16, 1, True, hyper(step[0], 1.0 / world),
+                                 pg.next_args())
+
+        for _ in range(args.warmup):
+            run()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        peers.check_status()
+        t = torch.tensor([e0.elapsed_time(e1) / args.iters], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        results[name] = float(t.item())
+        results["_epoch"] = pg.epoch
+        dist.barrier()
+
+    if rank == 0:
+        peak_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        hbm = float(json.load(open(peak_path))["hbm_gbs"]) if os.path.exists(peak_path) else 6650.0
+        link = 770.0
+        out = {"bench": "fused reduce-scatter + AdamW-24", "n_gpus": world, "grad_elems_per_rank": n,
+               "shard_elems": shard}
+        hbm_ms = shard * 14.25 / (hbm * 1e9) * 1e3
+        for name, ms_ in results.items():
+            if name.startswith("_"):
+                continue
+            rec = {"ms": round(ms_, 4)}
+            if name != "nccl_then_step":
+                inbound = shard * 2 * ((world - 1) if name == "fused_peer_loads" else (1 if world > 1 else 0))
+                link_ms = inbound / (link * 1e9) * 1e3
+                roof = max(link_ms, hbm_ms)
+                rec.update({"nvlink_inbound_MB": round(inbound / 1e6, 1), "roofline_ms": round(roof, 4),
+                            "bound": "nvlink" if link_ms > hbm_ms else "hbm",
+                            "frac_of_roofline": round(roof / ms_, 3)})
+            out[name] = rec
+        print(json.dumps(out), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
