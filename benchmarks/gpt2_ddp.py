@@ -38,6 +38,8 @@ def main():
     ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--comm-ctas", type=int, default=0, help="fused: grid cap of the all-reduce + update kernel")
     ap.add_argument("--multicast", action="store_true", help="fused: NVSwitch multimem.ld_reduce")
+    ap.add_argument("--two-shot", default="auto", choices=["auto", "on", "off"],
+                    help="fused: reduce + broadcast then local step for large buckets (auto: more than 2 GPUs)")
     args = ap.parse_args()
     if args.mode == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
@@ -78,7 +80,8 @@ def main():
     if args.mode == "fused":
         from flashoptim_b200.parallel import fuse_ddp_allreduce
 
-        state = fuse_ddp_allreduce(ddp, opt, use_multicast=args.multicast, max_ctas=args.comm_ctas)
+        state = fuse_ddp_allreduce(ddp, opt, use_multicast=args.multicast, max_ctas=args.comm_ctas,
+                                   two_shot={"auto": None, "on": True, "off": False}[args.two_shot])
 
     b, s = args.micro_batch, args.seq_len
     g = torch.Generator().manual_seed(99 + rank)
@@ -119,6 +122,7 @@ def main():
             "tokens_per_s": round(world * b * s / (ms * 1e-3), 1), "peak_gib_per_gpu": round(gib, 2),
             "loss": float(loss), "steps": args.steps, "warmup": args.warmup,
             "buckets_fused_per_step": (state.buckets_fused // (args.steps + args.warmup)) if state else 0,
+            "buckets_two_shot_per_step": (state.buckets_two_shot // (args.steps + args.warmup)) if state else 0,
         }), flush=True)
     dist.destroy_process_group()
 

@@ -157,6 +157,12 @@ int fo_momentum_step_peer(const FoSeg* segs, const int32_t* chunk_begin, int n_s
 // out[i] = scale * sum_r grad[r][src_offset_bytes + i] for n elements (no update).
 int fo_reduce_peer(int64_t n, int64_t src_offset_bytes, void* out, int dtype, float scale,
                    const FoCommArgs* comm, void* stream);
+// First shot of a two-shot all-reduce: rank r averages slice r (of `world` slices) of the n
+// elements at src_offset_bytes of every rank's buffer and stores it at dst_offset_bytes of
+// EVERY rank's buffer.  Once all ranks have published done(epoch), each buffer holds the full
+// averaged vector at dst_offset_bytes.
+int fo_reduce_bcast_peer(int64_t n, int64_t src_offset_bytes, int64_t dst_offset_bytes, int dtype,
+                         float scale, const FoCommArgs* comm, void* stream);
 // All-gather inside the symmetric buffer: every rank pulls slot s (slot_bytes
 // each, a multiple of 16) from rank s into its own copy.
 int fo_allgather_peer(int64_t slot_bytes, const FoCommArgs* comm, void* stream);

@@ -297,6 +297,55 @@ __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
   end_signal(A);
 }
 
+// Two-shot all-reduce, first shot: rank r averages slice r of the n elements at
+// `src_off` of every rank's buffer and stores the result into the same slice at
+// `dst_off` of EVERY rank's buffer (peer stores, or one multimem.st through the
+// switch).  After all ranks published done(epoch) each buffer holds the complete
+// averaged vector at `dst_off`; a local step kernel then reads it from its own HBM.
+__device__ __forceinline__ void multimem_st16(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
+    reduce_bcast_peer_kernel(int64_t n, int64_t src_off, int64_t dst_off, float scale,
+                             const __grid_constant__ FoCommArgs A) {
+  if (!start_barrier(A)) return;
+  // slices are multiples of 8 elements so that every unit of a slice is whole
+  const int64_t slice = ((n + (int64_t)A.world * kUnit - 1) / ((int64_t)A.world * kUnit)) * kUnit;
+  const int64_t begin = slice * A.rank;
+  const int64_t end = begin + slice < n ? begin + slice : n;
+  const int64_t n_units = end > begin ? (end - begin + kUnit - 1) / kUnit : 0;
+  const bool aligned = ((src_off | dst_off) & 15) == 0;
+  for (int64_t u = (int64_t)blockIdx.x * kCommThreads + threadIdx.x; u < n_units;
+       u += (int64_t)gridDim.x * kCommThreads) {
+    const int64_t base = begin + u * kUnit;
+    const int64_t left = end - base;
+    const int cnt = left >= kUnit ? kUnit : (int)left;
+    const bool vec = aligned && cnt == kUnit;
+    float2 g[4], s[4], back[4];
+    reduce_unit<T>(A, src_off + base * (int64_t)sizeof(T), cnt, vec, g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] = mul2(g[i], splat2(scale));
+    Raw8<T> r;
+    pack8<T>(s, r, back);
+    const int64_t off = dst_off + base * (int64_t)sizeof(T);
+    if (vec && A.multicast != nullptr) {
+      char* d = static_cast<char*>(const_cast<void*>(A.multicast)) + off;
+      multimem_st16(d, r.v);
+      if constexpr (sizeof(T) == 4) multimem_st16(d + 16, r.w);
+    } else {
+      for (int p = 0; p < A.world; ++p) {
+        T* d = reinterpret_cast<T*>(static_cast<char*>(const_cast<void*>(A.grad[p])) + off);
+        store_raw8<T>(r, d, cnt, vec);
+      }
+    }
+  }
+  end_signal(A);
+}
+
 // All-gather by pulling: rank r copies slot s of rank s's buffer (at s * slot_bytes)
 // into slot s of its own buffer, for every s != r.  Buffers are symmetric.
 __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
@@ -447,6 +496,31 @@ extern "C" int fo_reduce_peer(int64_t n, int64_t src_offset_bytes, void* out, in
       break;
     case FO_FP32:
       fo::reduce_peer_kernel<<<grid, fo::kCommThreads, 0, st>>>(n, src_offset_bytes, (float*)out, scale, *comm);
+      break;
+    default: return (int)cudaErrorInvalidValue;
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fo_reduce_bcast_peer(int64_t n, int64_t src_offset_bytes, int64_t dst_offset_bytes, int dtype,
+                                    float scale, const FoCommArgs* comm, void* stream) {
+  if (!fo::args_ok(comm)) return (int)cudaErrorInvalidValue;
+  if (n <= 0) return 0;
+  const int64_t per_rank = (n + comm->world - 1) / comm->world;
+  const int grid = fo::comm_grid((per_rank + fo::kCommChunk - 1) / fo::kCommChunk, comm);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case FO_BF16:
+      fo::reduce_bcast_peer_kernel<__nv_bfloat16><<<grid, fo::kCommThreads, 0, st>>>(n, src_offset_bytes,
+                                                                                      dst_offset_bytes, scale, *comm);
+      break;
+    case FO_FP16:
+      fo::reduce_bcast_peer_kernel<__half><<<grid, fo::kCommThreads, 0, st>>>(n, src_offset_bytes, dst_offset_bytes,
+                                                                               scale, *comm);
+      break;
+    case FO_FP32:
+      fo::reduce_bcast_peer_kernel<float><<<grid, fo::kCommThreads, 0, st>>>(n, src_offset_bytes, dst_offset_bytes,
+                                                                              scale, *comm);
       break;
     default: return (int)cudaErrorInvalidValue;
   }

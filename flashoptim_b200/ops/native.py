@@ -141,6 +141,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     ]
     lib.fo_reduce_peer.restype = c_int
     lib.fo_reduce_peer.argtypes = [c_int64, c_int64, c_void_p, c_int, c_float, POINTER(FoCommArgs), c_void_p]
+    lib.fo_reduce_bcast_peer.restype = c_int
+    lib.fo_reduce_bcast_peer.argtypes = [c_int64, c_int64, c_int64, c_int, c_float, POINTER(FoCommArgs), c_void_p]
     lib.fo_allgather_peer.restype = c_int
     lib.fo_allgather_peer.argtypes = [c_int64, POINTER(FoCommArgs), c_void_p]
     lib.fo_comm_signal.restype = c_int

@@ -441,6 +441,34 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
                 self._pre_step_many([it[2] for it in items])
                 self._fused_step(items, group, gi, peer=peer)
 
+    @torch.no_grad()
+    def step_with_grads(self, params: list[torch.Tensor], grads: list[torch.Tensor]) -> None:
+        """Update ``params`` from explicitly given (already reduced) gradient tensors
+        instead of ``.grad``, with the fused kernels on the current stream, and mark them
+        so that the following ``step()`` / ``step_param()`` leaves them alone once."""
+        index_of = {id(p): gi for gi, g in enumerate(self.param_groups) for p in g["params"]}
+        by_group: dict[int, list] = {}
+        for p, g in zip(params, grads):
+            by_group.setdefault(index_of[id(p)], []).append((p, g))
+        for gi, pairs in by_group.items():
+            group = self.param_groups[gi]
+            items = []
+            for p, g in pairs:
+                self._ensure_state_initialized(p, group)
+                p_local = local_tensor(p)
+                if p_local.numel() < 1 or not p.requires_grad:
+                    continue
+                if not (p_local.is_cuda and p_local.is_contiguous() and g.is_contiguous()
+                        and g.dtype == p_local.dtype and g.numel() == p_local.numel()):
+                    raise RuntimeError("step_with_grads needs contiguous CUDA tensors of the parameter's dtype")
+                if self._check_numerics:
+                    self._check_param_numerics(p, group["lr"], group["master_bytewidth"])
+                items.append((p_local, g, self.state[p]))
+                self._peer_stepped.add(id(p))
+            if items:
+                self._pre_step_many([it[2] for it in items])
+                self._fused_step(items, group, gi)
+
     def zero_grad(self, set_to_none: bool = True) -> None:
         if self._gradient_release:
             warnings.warn(

@@ -5,8 +5,12 @@ When a gradient bucket is ready the hook copies it into this rank's slice of a
 symmetric NVLink arena and, on a side stream, launches one kernel that reads
 the matching slice of every rank, averages in fp32 in rank order (all replicas
 therefore compute bit-identical values) and applies the optimizer update to the
-bucket's parameters and replicated states in the same pass.  NCCL is not
-involved; the averaged gradient never exists in HBM unless ``write_back=True``.
+bucket's parameters and replicated states in the same pass (one-shot).  NCCL is
+not involved; the averaged gradient never exists in HBM unless
+``write_back=True``.  With more than two ranks large buckets go two-shot: a
+reduce + broadcast kernel assembles the averaged bucket in every rank's arena
+(each slice is computed once, so replicas still agree bit for bit) and a local
+multi-tensor step consumes it.
 
 The reference cannot step inside a DDP hook at all (it rejects gradient release
 for DDP, ``flashoptim/optimizers.py:3111-3123``): PyTorch's reducer owns the
@@ -41,6 +45,8 @@ class FusedDDPState:
         use_multicast: bool = False,
         write_back: bool = False,
         max_ctas: int = 0,
+        two_shot_min_bytes: int = 1 << 20,
+        two_shot: Optional[bool] = None,
     ):
         params = [p for p in ddp_model.parameters() if p.requires_grad]
         if not params:
@@ -53,13 +59,19 @@ class FusedDDPState:
                                max_ctas=max_ctas)
         # every bucket gets a 256-byte aligned slice; one slice per parameter is the worst case
         total = sum(p.numel() * p.element_size() for p in params) + 256 * (len(params) + 1)
-        self.arena = self.peers.allocate(total)
+        # one-shot buckets use the first half (raw gradients); two-shot buckets also use the
+        # same offset in the second half, where the averaged gradients are assembled
+        self.half = (total + 255) // 256 * 256
+        self.two_shot = (self.peers.world > 2) if two_shot is None else bool(two_shot)
+        self.two_shot_min_bytes = two_shot_min_bytes
+        self.arena = self.peers.allocate(self.half * (2 if self.two_shot else 1))
         ready, done = self.peers.new_channels()
         self.grads = PeerGradients(self.peers, self.arena, ready, done, grad_scale=1.0 / self.peers.world, key=id(self))
         self.side = torch.cuda.Stream(device=params[0].device)
         self.cursor = 0
         self.region_epoch: dict[int, int] = {}
         self.buckets_fused = 0
+        self.buckets_two_shot = 0
         optimizer._post_step_callbacks.append(self._join)
 
     def _join(self) -> None:
@@ -72,7 +84,7 @@ class FusedDDPState:
         nbytes = buf.numel() * buf.element_size()
         off = self.cursor
         self.cursor += (nbytes + 255) // 256 * 256
-        if self.cursor > self.arena.nbytes:
+        if self.cursor > self.half:
             raise RuntimeError("gradient buckets exceed the symmetric arena")
         cur = torch.cuda.current_stream()
         # peers must have finished reading what this region held in the previous step
@@ -85,6 +97,32 @@ class FusedDDPState:
         params = bucket.parameters()
         base = buf.data_ptr()
         self.grads.offsets = {id(p): off + (g.data_ptr() - base) for p, g in zip(params, bucket.gradients())}
+        if self.two_shot and nbytes >= self.two_shot_min_bytes:
+            # two-shot: each rank averages 1/world of the bucket and stores it into every
+            # rank's second half; after all "done" flags the whole averaged bucket is local
+            # and one local multi-tensor step consumes it.  Per GPU this moves 2(W-1)/W of the
+            # bucket over NVLink instead of W-1 times the bucket.
+            import ctypes
+
+            from ..ops import native
+
+            with torch.cuda.stream(self.side):
+                args = self.grads.next_args()
+                rc = native.load().fo_reduce_bcast_peer(
+                    buf.numel(), off, self.half + off, native.DTYPE_CODE[buf.dtype], 1.0 / self.peers.world,
+                    ctypes.byref(args), native.stream_ptr(self.peers.device))
+                native.check(rc, "fo_reduce_bcast_peer")
+                self.peers.wait(args, self.grads.done_channel)
+                reduced = self.arena.view(self.half + off, buf.numel(), buf.dtype)
+                views = [reduced[(g.data_ptr() - base) // buf.element_size():][:g.numel()]
+                         for g in bucket.gradients()]
+                self.optimizer.step_with_grads(list(params), views)
+            self.region_epoch[off] = self.grads.epoch
+            self.buckets_fused += 1
+            self.buckets_two_shot += 1
+            fut2: torch.futures.Future = torch.futures.Future()
+            fut2.set_result(buf)
+            return fut2
         if self.write_back:
             self.grads.grad_out, self.grads.grad_out_sub = buf, off
         with torch.cuda.stream(self.side):
@@ -109,6 +147,8 @@ def fuse_ddp_allreduce(
     use_multicast: bool = False,
     write_back: bool = False,
     max_ctas: int = 0,
+    two_shot_min_bytes: int = 1 << 20,
+    two_shot: Optional[bool] = None,
 ) -> FusedDDPState:
     """Fuse DDP's per-bucket gradient all-reduce with ``optimizer``'s update.
 
@@ -119,9 +159,13 @@ def fuse_ddp_allreduce(
     into the bucket (needed only if something else reads ``p.grad``).
     ``use_multicast`` fetches through NVSwitch ``multimem.ld_reduce``; the default
     uses peer loads in rank order, which guarantees bit-identical replicas.
+    With more than two ranks, buckets of at least ``two_shot_min_bytes`` take the two-shot
+    route (reduce 1/world of the bucket, store it to every rank, then one local step);
+    smaller ones the one-shot kernel (``two_shot`` forces the choice).
     """
     if not isinstance(ddp_model, DDP):
         raise TypeError("fuse_ddp_allreduce expects a DistributedDataParallel model")
-    state = FusedDDPState(ddp_model, optimizer, group, timeout_s, use_multicast, write_back, max_ctas)
+    state = FusedDDPState(ddp_model, optimizer, group, timeout_s, use_multicast, write_back, max_ctas,
+                          two_shot_min_bytes, two_shot)
     ddp_model.register_comm_hook(state, state.hook)
     return state

@@ -121,7 +121,7 @@ def test_peer_adam_kernel_two_gpus_multimem():
     run_distributed(_peer_kernel_worker, world_size=2, backend="nccl", args=(True,))
 
 
-def _ddp_worker(rank, world):
+def _ddp_worker(rank, world, two_shot=False):
     from torch.nn.parallel import DistributedDataParallel as DDP
 
     from flashoptim_b200 import FlashAdamW, FlashLion
@@ -134,7 +134,7 @@ def _ddp_worker(rank, world):
         fused = DDP(_net(dev), device_ids=[rank], gradient_as_bucket_view=True, bucket_cap_mb=0.05)
         o1 = cls(plain.parameters(), **kw)
         o2 = cls(fused.parameters(), **kw)
-        state = fuse_ddp_allreduce(fused, o2)
+        state = fuse_ddp_allreduce(fused, o2, two_shot=two_shot, two_shot_min_bytes=1024)
         tol = get_tolerances(torch.bfloat16, True)
         for step, (x, y) in enumerate(_batches(world)):
             xs = x[rank * 8:(rank + 1) * 8].to(dev, torch.bfloat16)
@@ -162,11 +162,17 @@ def _ddp_worker(rank, world):
                     break
         if state.buckets_fused < 4:
             errors.append(f"{cls.__name__}: only {state.buckets_fused} buckets went through the fused hook")
+        if two_shot and state.buckets_two_shot < 4:
+            errors.append(f"{cls.__name__}: only {state.buckets_two_shot} buckets took the two-shot route")
     return errors
 
 
 def test_fused_ddp_matches_nccl_ddp():
     run_distributed(_ddp_worker, world_size=2, backend="nccl")
+
+
+def test_fused_ddp_two_shot_matches_nccl_ddp():
+    run_distributed(_ddp_worker, world_size=2, backend="nccl", args=(True,))
 
 
 def _fsdp_worker(rank, world):

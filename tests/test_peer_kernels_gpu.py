@@ -170,6 +170,30 @@ def test_reduce_and_allgather_kernels():
         assert torch.equal(bufs[2][s * slot:(s + 1) * slot], before[s][s * slot:(s + 1) * slot])
 
 
+@pytest.mark.parametrize("n", [4096 * 4, 10007])
+def test_two_shot_reduce_broadcast_kernel(n):
+    """Each emulated rank averages its slice and stores it into every rank's second half."""
+    world = 4
+    lib = native.load()
+    half = (n * 2 + 255) // 256 * 256
+    groups, bufs, pads = _emulated(world, 2 * half)
+    gen = torch.Generator(device=DEV).manual_seed(4)
+    for b in bufs:
+        b[:n * 2].view(torch.bfloat16).copy_(torch.randn(n, device=DEV, generator=gen) * 1e-3)
+    want = sum(b[:n * 2].view(torch.bfloat16).float() for b in bufs) / world
+    _publish_all(pads, 0, 1)
+    for r in range(world):
+        buf = SymmBuffer(bufs[r], [b.data_ptr() for b in bufs], 0)
+        a = groups[r].comm_args(buf, 1, 0, 1, pads=[q.data_ptr() for q in pads])
+        native.check(lib.fo_reduce_bcast_peer(n, 0, half, native.FO_BF16, 1.0 / world, ctypes.byref(a),
+                                              torch.cuda.current_stream().cuda_stream), "reduce_bcast")
+        groups[r].check_status()
+    for b in bufs:  # every rank now holds the complete averaged vector
+        got = b[half:half + n * 2].view(torch.bfloat16).float()
+        assert torch.allclose(got, want, rtol=2 ** -7, atol=1e-9)
+        assert torch.equal(got, bufs[0][half:half + n * 2].view(torch.bfloat16).float())
+
+
 def test_wait_that_nothing_satisfies_times_out_and_leaves_state_untouched():
     world, n = 2, 4096
     groups, bufs, pads = _emulated(world, n * 2, timeout_s=0.05)
