@@ -468,3 +468,25 @@ def test_params_without_grad_and_empty_params(device):
     for p in (a, b, c, frozen):
         assert "exp_avg" in opt.state[p] and "step" in opt.state[p]
     assert int(opt.state[a]["step"]) == 1 and int(opt.state[b]["step"]) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["adamw", "lion", "sgdw"])
+def test_step_with_explicit_gradients_equals_step(name):
+    """``step_with_grads`` (used by the two-shot DDP route) updates like ``step()`` and makes
+    the following ``step()`` skip those parameters once."""
+    m1 = _model("cuda", torch.bfloat16, seed=11)
+    m2 = copy.deepcopy(m1)
+    o1 = _make(name, m1.parameters(), 24, True)
+    o2 = _make(name, m2.parameters(), 24, True)
+    x, y = _data("cuda", torch.bfloat16)
+    for _ in range(3):
+        nn.functional.cross_entropy(m1(x).float(), y).backward()
+        o1.step(); o1.zero_grad()
+        nn.functional.cross_entropy(m2(x).float(), y).backward()
+        params = list(m2.parameters())
+        o2.step_with_grads(params, [p.grad.clone() for p in params])
+        o2.step()  # must not apply the gradients a second time
+        o2.zero_grad()
+    for a, b in zip(m1.parameters(), m2.parameters()):
+        assert torch.equal(a, b)
