@@ -10,11 +10,13 @@ master weights, 8-bit states).  Timed on the device with CUDA events, max over
 ranks; every iteration touches far more than the 126 MB L2.
 
 Roofline of the fused kernel = the slower of
-  * NVLink: bytes that must arrive from peers / 770 GB/s (measured peer-copy rate):
-    peer loads bring (world-1) rows of shard*2 bytes; multimem.ld_reduce brings one
-    reduced row (the switch adds), i.e. shard*2 bytes;
-  * HBM: shard * (12.25 + 2) bytes (update traffic + this rank's own row, read by the
-    switch or by the kernel) / measured copy bandwidth.
+  * NVLink: bytes per direction per GPU / 770 GB/s (measured peer-copy rate).  With peer
+    loads a rank receives (world-1) rows of shard*2 bytes and serves as many to its
+    peers.  With multimem.ld_reduce the switch adds, so a rank receives one reduced row,
+    but its memory is still read once for every other rank's row: (world-1)*shard*2 bytes
+    leave each GPU either way, and that direction is the bound;
+  * HBM: shard * (12.25 + 2) bytes (update traffic + this rank's own row) / measured copy
+    bandwidth.
 """
 
 from __future__ import annotations
@@ -125,9 +127,11 @@ def main():
             rec = {"ms": round(ms_, 4)}
             if name != "nccl_then_step":
                 inbound = shard * 2 * ((world - 1) if name == "fused_peer_loads" else (1 if world > 1 else 0))
-                link_ms = inbound / (link * 1e9) * 1e3
+                outbound = shard * 2 * (world - 1)
+                link_ms = max(inbound, outbound) / (link * 1e9) * 1e3
                 roof = max(link_ms, hbm_ms)
-                rec.update({"nvlink_inbound_MB": round(inbound / 1e6, 1), "roofline_ms": round(roof, 4),
+                rec.update({"nvlink_inbound_MB": round(inbound / 1e6, 1),
+                            "nvlink_outbound_MB": round(outbound / 1e6, 1), "roofline_ms": round(roof, 4),
                             "bound": "nvlink" if link_ms > hbm_ms else "hbm",
                             "frac_of_roofline": round(roof / ms_, 3)})
             out[name] = rec
