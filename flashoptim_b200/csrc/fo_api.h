@@ -143,8 +143,9 @@ typedef struct FoCommArgs {
   int max_ctas;  // upper bound on the launch grid (0: fill the GPU); NVLink-bound work needs few SMs
 } FoCommArgs;
 
-// Elements per CTA iteration of the peer kernels (for the chunk prefix).
-int fo_comm_chunk_elems(void);
+// Elements per CTA iteration of the peer step kernels for a group of `world` ranks (for
+// the chunk prefix): the fewer ranks, the more units a thread keeps in flight.
+int fo_comm_chunk_elems(int world);
 
 // `segs` and `chunk_begin` are DEVICE pointers.  The gradient of every element
 // is hyper->grad_scale times the sum over ranks (pass 1 / world for a mean).

@@ -128,32 +128,28 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_f32x4(const void* mc_addr) {
   return v;
 }
 
-// Sum of the W copies of one unit, in fp32, in rank order.  `off` is the byte
-// offset of the unit inside every rank's buffer.
-template <typename T>
-__device__ __forceinline__ void reduce_unit(const FoCommArgs& A, int64_t off, int cnt, bool vec,
-                                            float2 (&g)[4]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) g[i] = make_float2(0.f, 0.f);
+// Remote part of one unit: the W copies (peer loads) or the switch-reduced copy
+// (multimem) are requested here and only consumed by peer_sum(), so a thread can
+// have the loads of several units in flight.  `off` is the byte offset of the
+// unit inside every rank's buffer; kPeers bounds the world size at compile time.
+template <typename T, int kPeers>
+__device__ __forceinline__ void peer_load(const FoCommArgs& A, int64_t off, int cnt, bool vec,
+                                          Raw8<T> (&r)[kPeers]) {
   if (cnt <= 0) return;
   if (vec && A.multicast != nullptr) {
-    Raw8<T> r;
     const char* a = static_cast<const char*>(A.multicast) + off;
     if constexpr (sizeof(T) == 4) {
-      r.v = multimem_ld_reduce_f32x4(a);
-      r.w = multimem_ld_reduce_f32x4(a + 16);
+      r[0].v = multimem_ld_reduce_f32x4(a);
+      r[0].w = multimem_ld_reduce_f32x4(a + 16);
     } else if constexpr (Elem<T>::kMant == 7) {
-      r.v = multimem_ld_reduce_bf16x8(a);
+      r[0].v = multimem_ld_reduce_bf16x8(a);
     } else {
-      r.v = multimem_ld_reduce_f16x8(a);
+      r[0].v = multimem_ld_reduce_f16x8(a);
     }
-    unpack8<T>(r, g);
     return;
   }
-  // all loads first, then the adds: W independent requests in flight per thread
-  Raw8<T> r[FO_MAX_PEERS];
 #pragma unroll
-  for (int p = 0; p < FO_MAX_PEERS; ++p) {
+  for (int p = 0; p < kPeers; ++p) {
     if (p < A.world) {
       const T* src = reinterpret_cast<const T*>(static_cast<const char*>(A.grad[p]) + off);
       r[p].v = make_uint4(0, 0, 0, 0);
@@ -162,8 +158,20 @@ __device__ __forceinline__ void reduce_unit(const FoCommArgs& A, int64_t off, in
       else load_raw8_partial<T>(r[p], src, cnt);
     }
   }
+}
+// Sum in fp32, in rank order (every replica adds in the same order).
+template <typename T, int kPeers>
+__device__ __forceinline__ void peer_sum(const FoCommArgs& A, int cnt, bool vec, const Raw8<T> (&r)[kPeers],
+                                         float2 (&g)[4]) {
 #pragma unroll
-  for (int p = 0; p < FO_MAX_PEERS; ++p) {
+  for (int i = 0; i < 4; ++i) g[i] = make_float2(0.f, 0.f);
+  if (cnt <= 0) return;
+  if (vec && A.multicast != nullptr) {
+    unpack8<T>(r[0], g);
+    return;
+  }
+#pragma unroll
+  for (int p = 0; p < kPeers; ++p) {
     if (p < A.world) {
       float2 x[4];
       unpack8<T>(r[p], x);
@@ -171,6 +179,13 @@ __device__ __forceinline__ void reduce_unit(const FoCommArgs& A, int64_t off, in
       for (int i = 0; i < 4; ++i) g[i] = add2(g[i], x[i]);
     }
   }
+}
+template <typename T>
+__device__ __forceinline__ void reduce_unit(const FoCommArgs& A, int64_t off, int cnt, bool vec,
+                                            float2 (&g)[4]) {
+  Raw8<T> r[FO_MAX_PEERS];
+  peer_load<T, FO_MAX_PEERS>(A, off, cnt, vec, r);
+  peer_sum<T, FO_MAX_PEERS>(A, cnt, vec, r, g);
 }
 
 struct CommWalker {
@@ -218,55 +233,85 @@ __device__ __forceinline__ void store_grad_out(const FoCommArgs& A, int64_t goff
   store_raw8<T>(r, dst, cnt, v);
 }
 
-template <typename T, int kErr, bool kQ>
-__global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
-    adam_peer_kernel(const FoSeg* __restrict__ segs, const int32_t* __restrict__ cb, int total_chunks,
-                     const __grid_constant__ FoAdamHyper H, const __grid_constant__ FoCommArgs A) {
-  if (!start_barrier(A)) return;
-  using Regs = UnitRegs<T, kErr, 2, kQ>;
+// Units per thread by world size: the fewer ranks, the fewer remote loads one unit
+// issues, so more units are put in flight per thread (2 ranks: 4 units, 3-4 ranks: 2,
+// 5-8 ranks: 1); remote requests in flight per thread stay at 8 x 16 bytes.
+template <int kU>
+struct PeerCfg {
+  static constexpr int kPeers = FO_MAX_PEERS / kU;
+  static constexpr int kChunk = kCommThreads * kUnit * kU;
+  static constexpr int kCtas = kU == 1 ? kCommCtasPerSm : 2;
+};
+
+template <typename T, int kErr, int kStates, bool kQ, int kU, typename Hyper, typename Update>
+__device__ __forceinline__ void peer_step_body(const FoSeg* segs, const int32_t* cb, int total_chunks,
+                                               const Hyper& H, const FoCommArgs& A, Update update) {
+  using Regs = UnitRegs<T, kErr, kStates, kQ>;
+  constexpr int kPeers = PeerCfg<kU>::kPeers;
   CommWalker w(segs, cb);
   for (int c = blockIdx.x; c < total_chunks; c += gridDim.x) {
     w.seek(c);
-    const int64_t base = (int64_t)(c - w.seg_begin) * kCommChunk + (int64_t)threadIdx.x * kUnit;
-    Regs r;
-    load_unit_state(r, w.S, base, w.vec);
-    const bool vec = w.vec && r.cnt == kUnit;
-    const int64_t goff = (int64_t)reinterpret_cast<intptr_t>(w.S.g) + base * (int64_t)sizeof(T);
-    float2 p[4], g[4], m[4], v[4];
-    reduce_unit<T>(A, goff, r.cnt, vec, g);
-    store_grad_out<T>(A, goff, r.cnt, vec, g, H.grad_scale);
-    widen_unit(r, p, m, v);
-    adam_update8<kQ>(p, g, m, v, H);
-    store_unit(r, w.S, base, w.vec, p, m, v);
+    const int64_t chunk_base = (int64_t)(c - w.seg_begin) * PeerCfg<kU>::kChunk;
+    const int64_t g0 = (int64_t)reinterpret_cast<intptr_t>(w.S.g);
+    Raw8<T> remote[kU][kPeers];
+    int cnt[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int64_t base = chunk_base + (int64_t)(u * kCommThreads + threadIdx.x) * kUnit;
+      const int64_t left = w.S.n - base;
+      cnt[u] = left >= kUnit ? kUnit : (int)left;
+      peer_load<T, kPeers>(A, g0 + base * (int64_t)sizeof(T), cnt[u], w.vec && cnt[u] == kUnit, remote[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int64_t base = chunk_base + (int64_t)(u * kCommThreads + threadIdx.x) * kUnit;
+      Regs r;
+      load_unit_state(r, w.S, base, w.vec);
+      const bool vec = w.vec && r.cnt == kUnit;
+      float2 p[4], g[4], m[4], v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) m[i] = v[i] = make_float2(0.f, 0.f);
+      peer_sum<T, kPeers>(A, r.cnt, vec, remote[u], g);
+      store_grad_out<T>(A, g0 + base * (int64_t)sizeof(T), r.cnt, vec, g, H.grad_scale);
+      widen_unit(r, p, m, v);
+      update(p, g, m, v, H);
+      store_unit(r, w.S, base, w.vec, p, m, v);
+    }
   }
+}
+
+template <bool kQ>
+struct PeerAdamUpdate {
+  __device__ __forceinline__ void operator()(float2 (&p)[4], const float2 (&g)[4], float2 (&m)[4], float2 (&v)[4],
+                                             const FoAdamHyper& H) const {
+    adam_update8<kQ>(p, g, m, v, H);
+  }
+};
+template <bool kHasState>
+struct PeerMomentumUpdate {
+  __device__ __forceinline__ void operator()(float2 (&p)[4], const float2 (&g)[4], float2 (&m)[4], float2 (&v)[4],
+                                             const FoMomentumHyper& H) const {
+    momentum_update8(p, g, m, H, kHasState);
+  }
+};
+
+template <typename T, int kErr, bool kQ, int kU>
+__global__ void __launch_bounds__(kCommThreads, PeerCfg<kU>::kCtas)
+    adam_peer_kernel(const FoSeg* __restrict__ segs, const int32_t* __restrict__ cb, int total_chunks,
+                     const __grid_constant__ FoAdamHyper H, const __grid_constant__ FoCommArgs A) {
+  if (!start_barrier(A)) return;
+  peer_step_body<T, kErr, 2, kQ, kU>(segs, cb, total_chunks, H, A, PeerAdamUpdate<kQ>());
   end_signal(A);
 }
 
-template <typename T, int kErr, int kMode>
-__global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
+template <typename T, int kErr, int kMode, int kU>
+__global__ void __launch_bounds__(kCommThreads, PeerCfg<kU>::kCtas)
     momentum_peer_kernel(const FoSeg* __restrict__ segs, const int32_t* __restrict__ cb, int total_chunks,
                          const __grid_constant__ FoMomentumHyper H, const __grid_constant__ FoCommArgs A) {
   if (!start_barrier(A)) return;
   constexpr int kStates = kMode == FO_STATE_NONE ? 0 : 1;
   constexpr bool kQ = kMode == FO_STATE_Q8;
-  using Regs = UnitRegs<T, kErr, kStates, kQ>;
-  CommWalker w(segs, cb);
-  for (int c = blockIdx.x; c < total_chunks; c += gridDim.x) {
-    w.seek(c);
-    const int64_t base = (int64_t)(c - w.seg_begin) * kCommChunk + (int64_t)threadIdx.x * kUnit;
-    Regs r;
-    load_unit_state(r, w.S, base, w.vec);
-    const bool vec = w.vec && r.cnt == kUnit;
-    const int64_t goff = (int64_t)reinterpret_cast<intptr_t>(w.S.g) + base * (int64_t)sizeof(T);
-    float2 p[4], g[4], m[4], v[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) m[i] = v[i] = make_float2(0.f, 0.f);
-    reduce_unit<T>(A, goff, r.cnt, vec, g);
-    store_grad_out<T>(A, goff, r.cnt, vec, g, H.grad_scale);
-    widen_unit(r, p, m, v);
-    momentum_update8(p, g, m, H, kStates > 0);
-    store_unit(r, w.S, base, w.vec, p, m, v);
-  }
+  peer_step_body<T, kErr, kStates, kQ, kU>(segs, cb, total_chunks, H, A, PeerMomentumUpdate<(kStates > 0)>());
   end_signal(A);
 }
 
@@ -374,11 +419,13 @@ __global__ void wait_kernel(const __grid_constant__ FoCommArgs A, int channel) {
   if (threadIdx.x < A.world) wait_flag(A, channel, threadIdx.x, A.epoch);
 }
 
-static int comm_grid(int64_t work_ctas, const FoCommArgs* a) {
+static int units_for_world(int world) { return world <= 2 ? 4 : (world <= 4 ? 2 : 1); }
+
+static int comm_grid(int64_t work_ctas, const FoCommArgs* a, int ctas_per_sm = kCommCtasPerSm) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  int64_t g = (int64_t)sms * kCommCtasPerSm;
+  int64_t g = (int64_t)sms * ctas_per_sm;
   if (a && a->max_ctas > 0 && a->max_ctas < g) g = a->max_ctas;
   if (work_ctas < g) g = work_ctas;
   return g < 1 ? 1 : (int)g;
@@ -388,73 +435,90 @@ static bool args_ok(const FoCommArgs* a) {
   return a && a->world >= 1 && a->world <= FO_MAX_PEERS && a->rank >= 0 && a->rank < a->world && a->status;
 }
 
-template <typename T, int kErr>
+template <typename T, int kErr, int kU>
 static int launch_adam_peer_q(const FoSeg* s, const int32_t* cb, int total, const FoAdamHyper& H,
-                              const FoCommArgs& A, int quantized, int grid, cudaStream_t st) {
-  if (quantized) adam_peer_kernel<T, kErr, true><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
-  else adam_peer_kernel<T, kErr, false><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+                              const FoCommArgs& A, int quantized, cudaStream_t st) {
+  const int grid = comm_grid(total, &A, PeerCfg<kU>::kCtas);
+  if (quantized) adam_peer_kernel<T, kErr, true, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+  else adam_peer_kernel<T, kErr, false, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
   return (int)cudaGetLastError();
+}
+template <typename T, int kErr>
+static int launch_adam_peer_u(const FoSeg* s, const int32_t* cb, int total, const FoAdamHyper& H,
+                              const FoCommArgs& A, int quantized, cudaStream_t st) {
+  switch (units_for_world(A.world)) {
+    case 4: return launch_adam_peer_q<T, kErr, 4>(s, cb, total, H, A, quantized, st);
+    case 2: return launch_adam_peer_q<T, kErr, 2>(s, cb, total, H, A, quantized, st);
+  }
+  return launch_adam_peer_q<T, kErr, 1>(s, cb, total, H, A, quantized, st);
 }
 template <typename T>
 static int launch_adam_peer(const FoSeg* s, const int32_t* cb, int total, const FoAdamHyper& H,
-                            const FoCommArgs& A, int err, int quantized, int grid, cudaStream_t st) {
+                            const FoCommArgs& A, int err, int quantized, cudaStream_t st) {
   if constexpr (Elem<T>::kNarrow) {
-    if (err == 1) return launch_adam_peer_q<T, 1>(s, cb, total, H, A, quantized, grid, st);
-    if (err == 2) return launch_adam_peer_q<T, 2>(s, cb, total, H, A, quantized, grid, st);
+    if (err == 1) return launch_adam_peer_u<T, 1>(s, cb, total, H, A, quantized, st);
+    if (err == 2) return launch_adam_peer_u<T, 2>(s, cb, total, H, A, quantized, st);
   }
   if (err != 0) return (int)cudaErrorInvalidValue;
-  return launch_adam_peer_q<T, 0>(s, cb, total, H, A, quantized, grid, st);
+  return launch_adam_peer_u<T, 0>(s, cb, total, H, A, quantized, st);
 }
 
-template <typename T, int kErr>
+template <typename T, int kErr, int kU>
 static int launch_mom_peer_m(const FoSeg* s, const int32_t* cb, int total, const FoMomentumHyper& H,
-                             const FoCommArgs& A, int mode, int grid, cudaStream_t st) {
+                             const FoCommArgs& A, int mode, cudaStream_t st) {
+  const int grid = comm_grid(total, &A, PeerCfg<kU>::kCtas);
   switch (mode) {
     case FO_STATE_NONE:
-      momentum_peer_kernel<T, kErr, FO_STATE_NONE><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+      momentum_peer_kernel<T, kErr, FO_STATE_NONE, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
       break;
     case FO_STATE_Q8:
-      momentum_peer_kernel<T, kErr, FO_STATE_Q8><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+      momentum_peer_kernel<T, kErr, FO_STATE_Q8, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
       break;
     case FO_STATE_FULL:
-      momentum_peer_kernel<T, kErr, FO_STATE_FULL><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+      momentum_peer_kernel<T, kErr, FO_STATE_FULL, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
       break;
     default: return (int)cudaErrorInvalidValue;
   }
   return (int)cudaGetLastError();
 }
+template <typename T, int kErr>
+static int launch_mom_peer_u(const FoSeg* s, const int32_t* cb, int total, const FoMomentumHyper& H,
+                             const FoCommArgs& A, int mode, cudaStream_t st) {
+  switch (units_for_world(A.world)) {
+    case 4: return launch_mom_peer_m<T, kErr, 4>(s, cb, total, H, A, mode, st);
+    case 2: return launch_mom_peer_m<T, kErr, 2>(s, cb, total, H, A, mode, st);
+  }
+  return launch_mom_peer_m<T, kErr, 1>(s, cb, total, H, A, mode, st);
+}
 template <typename T>
 static int launch_mom_peer(const FoSeg* s, const int32_t* cb, int total, const FoMomentumHyper& H,
-                           const FoCommArgs& A, int err, int mode, int grid, cudaStream_t st) {
+                           const FoCommArgs& A, int err, int mode, cudaStream_t st) {
   if constexpr (Elem<T>::kNarrow) {
-    if (err == 1) return launch_mom_peer_m<T, 1>(s, cb, total, H, A, mode, grid, st);
-    if (err == 2) return launch_mom_peer_m<T, 2>(s, cb, total, H, A, mode, grid, st);
+    if (err == 1) return launch_mom_peer_u<T, 1>(s, cb, total, H, A, mode, st);
+    if (err == 2) return launch_mom_peer_u<T, 2>(s, cb, total, H, A, mode, st);
   }
   if (err != 0) return (int)cudaErrorInvalidValue;
-  return launch_mom_peer_m<T, 0>(s, cb, total, H, A, mode, grid, st);
+  return launch_mom_peer_u<T, 0>(s, cb, total, H, A, mode, st);
 }
 
 }  // namespace fo
 
-extern "C" int fo_comm_chunk_elems(void) { return fo::kCommChunk; }
+extern "C" int fo_comm_chunk_elems(int world) { return fo::kCommChunk * fo::units_for_world(world); }
 
 extern "C" int fo_adam_step_peer(const FoSeg* segs, const int32_t* chunk_begin, int n_seg, int total_chunks,
                                  int dtype, int err_bytes, int quantized, const FoAdamHyper* hyper,
                                  const FoCommArgs* comm, void* stream) {
   if (!fo::args_ok(comm) || !hyper) return (int)cudaErrorInvalidValue;
   if (n_seg <= 0 || total_chunks <= 0) return 0;
-  const int grid = fo::comm_grid(total_chunks, comm);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case FO_BF16:
       return fo::launch_adam_peer<__nv_bfloat16>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes,
-                                                 quantized, grid, st);
+                                                 quantized, st);
     case FO_FP16:
-      return fo::launch_adam_peer<__half>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, quantized,
-                                          grid, st);
+      return fo::launch_adam_peer<__half>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, quantized, st);
     case FO_FP32:
-      return fo::launch_adam_peer<float>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, quantized,
-                                         grid, st);
+      return fo::launch_adam_peer<float>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, quantized, st);
   }
   return (int)cudaErrorInvalidValue;
 }
@@ -464,18 +528,15 @@ extern "C" int fo_momentum_step_peer(const FoSeg* segs, const int32_t* chunk_beg
                                      const FoMomentumHyper* hyper, const FoCommArgs* comm, void* stream) {
   if (!fo::args_ok(comm) || !hyper) return (int)cudaErrorInvalidValue;
   if (n_seg <= 0 || total_chunks <= 0) return 0;
-  const int grid = fo::comm_grid(total_chunks, comm);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case FO_BF16:
       return fo::launch_mom_peer<__nv_bfloat16>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes,
-                                                state_mode, grid, st);
+                                                state_mode, st);
     case FO_FP16:
-      return fo::launch_mom_peer<__half>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, state_mode,
-                                         grid, st);
+      return fo::launch_mom_peer<__half>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, state_mode, st);
     case FO_FP32:
-      return fo::launch_mom_peer<float>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, state_mode,
-                                        grid, st);
+      return fo::launch_mom_peer<float>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes, state_mode, st);
   }
   return (int)cudaErrorInvalidValue;
 }

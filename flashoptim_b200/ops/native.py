@@ -128,7 +128,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.fo_maxabs.restype = c_int
     lib.fo_maxabs.argtypes = [c_void_p, c_int, c_int64, c_void_p, c_void_p]
     lib.fo_comm_chunk_elems.restype = c_int
-    lib.fo_comm_chunk_elems.argtypes = []
+    lib.fo_comm_chunk_elems.argtypes = [c_int]
     lib.fo_adam_step_peer.restype = c_int
     lib.fo_adam_step_peer.argtypes = [
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, POINTER(FoAdamHyper), POINTER(FoCommArgs),

@@ -116,6 +116,7 @@ class SegmentTable:
         self._host: Optional[np.ndarray] = None       # [n_seg, 8] int64, last uploaded image
         self._chunks: Optional[np.ndarray] = None     # [n_seg + 1] int32
         self._dev: Optional[torch.Tensor] = None      # uint8 device buffer: segs then chunk_begin
+        self._chunk = 0                               # chunk size the prefix was built for
         self.uploads = 0
 
     @staticmethod
@@ -138,8 +139,9 @@ class SegmentTable:
         n_seg = rows.shape[0]
         chunk = chunk or native.chunk_elems()
         same_shape = self._host is not None and self._host.shape == rows.shape
-        if not same_shape or not np.array_equal(self._host[:, 7], rows[:, 7]):
+        if not same_shape or chunk != self._chunk or not np.array_equal(self._host[:, 7], rows[:, 7]):
             self._chunks = self.chunk_prefix(rows[:, 7], chunk)
+            self._chunk = chunk
             changed = True
         else:
             changed = not np.array_equal(self._host, rows)
@@ -226,7 +228,7 @@ def launch_adam_peer(
     if rows.shape[0] == 0:
         return
     lib = native.load()
-    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(), force_device=True)
+    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(comm.world), force_device=True)
     h = hyper.to_c()
     with torch.cuda.device(table.device):
         rc = lib.fo_adam_step_peer(
@@ -251,7 +253,7 @@ def launch_momentum_peer(
     if rows.shape[0] == 0:
         return
     lib = native.load()
-    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(), force_device=True)
+    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(comm.world), force_device=True)
     h = hyper.to_c()
     with torch.cuda.device(table.device):
         rc = lib.fo_momentum_step_peer(
