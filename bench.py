@@ -57,8 +57,11 @@ def parse_args():
     ap.add_argument("--comm-ctas", type=int, default=0, help="grid cap of the fused reduce-scatter kernel")
     ap.add_argument("--own-all-gather", action="store_true",
                     help="fused path: FSDP2's parameter all-gather through this library's pull kernel")
-    ap.add_argument("--no-multicast", action="store_true",
-                    help="fused path: sum peer loads in fp32 instead of NVSwitch multimem.ld_reduce")
+    ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
+                    help="fused path: NVSwitch multimem.ld_reduce (on) or peer loads summed in fp32 (off); "
+                         "auto = peer loads up to 4 GPUs, multimem above (the faster one in the "
+                         "fused-collective microbenchmark at each size)")
+    ap.add_argument("--no-multicast", action="store_true", help="same as --multicast off")
     return ap.parse_args()
 
 
@@ -220,12 +223,15 @@ def main():
                              master_weight_bits=mwb, compress_state_dict=args.compress_state_dict)
     fused_comm = False
     fused_state = None
+    use_multicast = (world > 4) if args.multicast == "auto" else args.multicast == "on"
+    if args.no_multicast:
+        use_multicast = False
     if args.impl == "ours" and args.fused_comm == "auto":
         try:
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
-            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=60.0, max_ctas=args.comm_ctas, use_multicast=not args.no_multicast,
-                                                         own_all_gather=args.own_all_gather)
+            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=60.0, max_ctas=args.comm_ctas,
+                                                    use_multicast=use_multicast, own_all_gather=args.own_all_gather)
             fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
             if rank == 0:
@@ -348,7 +354,7 @@ def main():
                 "parallelism": f"fsdp2x{world}",
                 "optimizer": f"{'FlashLion' if args.optimizer == 'lion' else 'FlashAdamW'} mwb={mwb}",
                 "gradient_release": bool(args.gradient_release), "fused_comm": bool(fused_comm),
-                "fused_comm_multicast": bool(fused_comm and not args.no_multicast),
+                "fused_comm_multicast": bool(fused_comm and use_multicast),
                 "activation_checkpointing": bool(cfg.activation_checkpointing),
                 "l2": "working set (>= 16 GB of weights) far exceeds the 126 MB L2; no flush",
             },
