@@ -57,6 +57,9 @@ def parse_args():
     ap.add_argument("--comm-ctas", type=int, default=0, help="grid cap of the fused reduce-scatter kernel")
     ap.add_argument("--own-all-gather", action="store_true",
                     help="fused path: FSDP2's parameter all-gather through this library's pull kernel")
+    ap.add_argument("--push-params", action="store_true",
+                    help="fused path: the update kernel also stores the new parameters into every rank's "
+                         "all-gather buffer, so FSDP2's parameter all-gathers move no data")
     ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
                     help="fused path: NVSwitch multimem.ld_reduce (on) or peer loads summed in fp32 (off); "
                          "auto = peer loads up to 4 GPUs, multimem above (the faster one in the "
@@ -231,7 +234,8 @@ def main():
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
             fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=60.0, max_ctas=args.comm_ctas,
-                                                    use_multicast=use_multicast, own_all_gather=args.own_all_gather)
+                                                    use_multicast=use_multicast, own_all_gather=args.own_all_gather,
+                                                    push_params=args.push_params)
             fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
             if rank == 0:
@@ -355,6 +359,7 @@ def main():
                 "optimizer": f"{'FlashLion' if args.optimizer == 'lion' else 'FlashAdamW'} mwb={mwb}",
                 "gradient_release": bool(args.gradient_release), "fused_comm": bool(fused_comm),
                 "fused_comm_multicast": bool(fused_comm and use_multicast),
+                "fused_param_push": bool(fused_comm and args.push_params),
                 "activation_checkpointing": bool(cfg.activation_checkpointing),
                 "l2": "working set (>= 16 GB of weights) far exceeds the 126 MB L2; no flush",
             },

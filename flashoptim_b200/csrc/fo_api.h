@@ -129,6 +129,12 @@ enum { FO_MAX_PEERS = 8 };
 //   timeout_ns   limit of every device-side wait
 //   max_ctas     cap on the number of CTAs, so that a link-bound kernel running beside
 //                backward leaves the SMs to the GEMMs
+//   push         step kernels only, optional "all-gather on write": every updated parameter
+//                unit is also stored, in the parameter dtype, at byte offset
+//                (FoSeg.g + unit offset + param_out_delta) of param_out[r] for every rank r
+//                (or once through the multicast mapping param_out_mc), and the kernel then
+//                publishes push_epoch on pushed_channel.  A rank that waits for all ranks'
+//                pushed flags holds every rank's fresh parameters without an all-gather.
 typedef struct FoCommArgs {
   const void* grad[FO_MAX_PEERS];
   const void* multicast;
@@ -141,6 +147,12 @@ typedef struct FoCommArgs {
   int world, rank;
   int ready_channel, done_channel;
   int max_ctas;  // upper bound on the launch grid (0: fill the GPU); NVLink-bound work needs few SMs
+  int push;      // 0: no parameter push (the fields below are ignored)
+  void* param_out[FO_MAX_PEERS];
+  void* param_out_mc;
+  int64_t param_out_delta;
+  uint32_t push_epoch;
+  int pushed_channel;
 } FoCommArgs;
 
 // Elements per CTA iteration of the peer step kernels for a group of `world` ranks (for

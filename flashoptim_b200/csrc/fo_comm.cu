@@ -89,7 +89,8 @@ __device__ __forceinline__ void end_signal(const FoCommArgs& A) {
   __shared__ int last;
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
+    if (A.push) __threadfence_system();  // this CTA's stores into the peers' memory
+    else __threadfence();
     unsigned int n = atomicAdd(reinterpret_cast<unsigned int*>(A.status) + 2, 1u);
     last = (n == gridDim.x - 1);
     if (last) reinterpret_cast<unsigned int*>(A.status)[2] = 0;  // ready for the next launch
@@ -98,6 +99,7 @@ __device__ __forceinline__ void end_signal(const FoCommArgs& A) {
   if (last && threadIdx.x < A.world) {
     __threadfence_system();
     st_release_sys(A.pad[threadIdx.x] + A.done_channel * FO_MAX_PEERS + A.rank, A.epoch);
+    if (A.push) st_release_sys(A.pad[threadIdx.x] + A.pushed_channel * FO_MAX_PEERS + A.rank, A.push_epoch);
   }
 }
 
@@ -126,6 +128,12 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_f32x4(const void* mc_addr) {
                : "l"(mc_addr)
                : "memory");
   return v;
+}
+
+__device__ __forceinline__ void multimem_st16(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
 }
 
 // Remote part of one unit: the W copies (peer loads) or the switch-reduced copy
@@ -233,6 +241,29 @@ __device__ __forceinline__ void store_grad_out(const FoCommArgs& A, int64_t goff
   store_raw8<T>(r, dst, cnt, v);
 }
 
+// All-gather on write: the freshly narrowed parameter unit goes to the same offset of
+// every rank's parameter buffer (W peer stores, or one multimem.st replicated by the switch).
+template <typename T, int kPeers>
+__device__ __forceinline__ void push_param(const FoCommArgs& A, int64_t off, int cnt, bool vec,
+                                           const Raw8<T>& pn) {
+  if (cnt <= 0) return;
+  off += A.param_out_delta;
+  if (vec && A.param_out_mc != nullptr && (off & 15) == 0) {
+    char* d = static_cast<char*>(A.param_out_mc) + off;
+    multimem_st16(d, pn.v);
+    if constexpr (sizeof(T) == 4) multimem_st16(d + 16, pn.w);
+    return;
+  }
+#pragma unroll
+  for (int p = 0; p < kPeers; ++p) {
+    if (p < A.world) {
+      T* d = reinterpret_cast<T*>(static_cast<char*>(A.param_out[p]) + off);
+      const bool v = vec && ((reinterpret_cast<uintptr_t>(d) & 15) == 0);
+      store_raw8<T>(pn, d, cnt, v);
+    }
+  }
+}
+
 // Units per thread by world size: the fewer ranks, the fewer remote loads one unit
 // issues, so more units are put in flight per thread (2 ranks: 4 units, 3-4 ranks: 2,
 // 5-8 ranks: 1); remote requests in flight per thread stay at 8 x 16 bytes.
@@ -275,7 +306,9 @@ __device__ __forceinline__ void peer_step_body(const FoSeg* segs, const int32_t*
       store_grad_out<T>(A, g0 + base * (int64_t)sizeof(T), r.cnt, vec, g, H.grad_scale);
       widen_unit(r, p, m, v);
       update(p, g, m, v, H);
-      store_unit(r, w.S, base, w.vec, p, m, v);
+      Raw8<T> pn;
+      store_unit(r, w.S, base, w.vec, p, m, v, pn);
+      if (A.push) push_param<T, kPeers>(A, g0 + base * (int64_t)sizeof(T), r.cnt, vec, pn);
     }
   }
 }
@@ -347,12 +380,6 @@ __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
 // `dst_off` of EVERY rank's buffer (peer stores, or one multimem.st through the
 // switch).  After all ranks published done(epoch) each buffer holds the complete
 // averaged vector at `dst_off`; a local step kernel then reads it from its own HBM.
-__device__ __forceinline__ void multimem_st16(void* mc_addr, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
-               "r"(v.z), "r"(v.w)
-               : "memory");
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
     reduce_bcast_peer_kernel(int64_t n, int64_t src_off, int64_t dst_off, float scale,

@@ -163,14 +163,14 @@ __device__ __forceinline__ void widen_unit(const UnitRegs<T, kErr, kStates, kQ>&
   }
 }
 
-// Narrow and store parameter, correction and states.
+// Narrow and store parameter, correction and states.  `pn` returns the narrowed
+// parameter unit as stored (for callers that also send it elsewhere).
 template <typename T, int kErr, int kStates, bool kQ>
 __device__ __forceinline__ void store_unit(const UnitRegs<T, kErr, kStates, kQ>& r, const FoSeg& s,
                                            int64_t base, bool seg_vec, const float2 (&p)[4],
-                                           const float2 (&m)[4], const float2 (&v)[4]) {
+                                           const float2 (&m)[4], const float2 (&v)[4], Raw8<T>& pn) {
   // when kQ, `v` holds the square root of the second state (what its codes store)
   const bool vec = seg_vec && r.cnt == kUnit;
-  Raw8<T> pn;
   float2 back[4];
   pack8<T>(p, pn, back);
   store_raw8<T>(pn, static_cast<T*>(s.p) + base, r.cnt, vec);
@@ -219,6 +219,14 @@ __device__ __forceinline__ void store_unit(const UnitRegs<T, kErr, kStates, kQ>&
       store_raw8<T>(fn, static_cast<T*>(sp) + base, r.cnt, vec);
     }
   }
+}
+
+template <typename T, int kErr, int kStates, bool kQ>
+__device__ __forceinline__ void store_unit(const UnitRegs<T, kErr, kStates, kQ>& r, const FoSeg& s,
+                                           int64_t base, bool seg_vec, const float2 (&p)[4],
+                                           const float2 (&m)[4], const float2 (&v)[4]) {
+  Raw8<T> pn;
+  store_unit(r, s, base, seg_vec, p, m, v, pn);
 }
 
 // ---------------------------------------------------------------- update rules on 8 elements

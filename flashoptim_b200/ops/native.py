@@ -87,6 +87,12 @@ class FoCommArgs(Structure):
         ("ready_channel", c_int),
         ("done_channel", c_int),
         ("max_ctas", c_int),
+        ("push", c_int),
+        ("param_out", c_void_p * FO_MAX_PEERS),
+        ("param_out_mc", c_void_p),
+        ("param_out_delta", c_int64),
+        ("push_epoch", ctypes.c_uint32),
+        ("pushed_channel", c_int),
     ]
 
 

@@ -135,6 +135,8 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         # skips them once
         self._peer_stepped: set[int] = set()
         self._post_step_callbacks: list[Callable[[], None]] = []
+        # called with the parameters that a local (not collective-fused) update changed
+        self._local_update_listeners: list[Callable[[list[torch.Tensor]], None]] = []
 
         defaults = dict(defaults or {})
         defaults.update({"lr": lr, "master_bytewidth": master_bytewidth, "quantize": quantize})
@@ -341,6 +343,7 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         """Update ``params`` (all in ``group``).  State is created for every one of
         them; those without a gradient are otherwise left alone."""
         fused_items: list[tuple[torch.Tensor, torch.Tensor, dict[str, Any]]] = []
+        updated: list[torch.Tensor] = []
         for p in params:
             self._ensure_state_initialized(p, group)
             if self._peer_stepped and id(p) in self._peer_stepped:
@@ -357,6 +360,7 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
             g_local = local_tensor(p.grad)
             if p_local.numel() < 1:
                 continue
+            updated.append(p)
             if p_local.is_cuda and self._fused:
                 if not p_local.is_contiguous():
                     raise RuntimeError(
@@ -379,6 +383,9 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         if fused_items:
             self._pre_step_many([it[2] for it in fused_items])
             self._fused_step(fused_items, group, group_index)
+        if updated and self._local_update_listeners:
+            for fn in self._local_update_listeners:
+                fn(updated)
 
     @torch.no_grad()
     def step_param(self, p: torch.Tensor, group: Optional[dict[str, Any]] = None) -> None:
@@ -603,6 +610,7 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         self.__dict__.setdefault("_transient_state", {})
         self.__dict__.setdefault("_peer_stepped", set())
         self.__dict__.setdefault("_post_step_callbacks", [])
+        self.__dict__.setdefault("_local_update_listeners", [])
         self._tables.clear()
         self._transient_state.clear()
         opt_state = cast(dict[torch.Tensor, Any], state["state"])

@@ -12,6 +12,13 @@ The kernel runs on FSDP2's reduce-scatter stream, overlapped with backward
 compute, exactly where the reference's gradient-release hook would have run its
 per-tensor update after NCCL finished (``flashoptim/optimizers.py:3040-3047``).
 
+With ``push_params=True`` the same kernel also stores every freshly updated bf16/fp16
+parameter unit into a per-group symmetric buffer on every rank ("all-gather on write",
+NVLink peer stores or one ``multimem.st``).  That buffer is what FSDP2 is handed as its
+all-gather output, so the parameter all-gathers of the following forward and backward
+passes move no data: they wait for the ranks' "pushed" flags and return
+(:class:`PushedAllGather`).  The price is one unsharded copy of the parameters per rank.
+
 Parameters updated this way are skipped once by the next ``step()`` /
 ``step_param()``, so the usual training loop and gradient release keep working.
 Groups the kernel cannot serve (non-default divide factors, a reduce dtype
@@ -28,7 +35,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..optim.base import FlashOptimizer, local_tensor
-from .symm import PeerGradients, PeerGroup
+from .symm import ParamPush, PeerGradients, PeerGroup
 
 import ctypes
 
@@ -65,6 +72,7 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
         self.ctx = ctx
         self.fsdp_params = fsdp_params
         self._slot: Optional[PeerGradients] = None
+        self.gather: Optional["PushedAllGather"] = None  # receives the updated parameters
         w = ctx.peers.world
         self.row_numels = [fp.padded_sharded_param_size.numel() for fp in fsdp_params]
         self.input_numel = w * sum(self.row_numels)
@@ -99,6 +107,8 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
         )
         if not fused:
             self.ctx.fallbacks += 1
+            if self.gather is not None:
+                self.gather.invalidate()  # the parameters will change without a push
             return dist.reduce_scatter_tensor(output=output_tensor, input=input_tensor, group=group, op=op,
                                               async_op=async_op)
         peers = self.ctx.peers
@@ -111,7 +121,18 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
             off += n * esize
         slot.offsets = offsets
         slot.grad_out, slot.grad_out_sub = output_tensor, base
-        self.ctx.optimizer.step_from_peers([fp.sharded_param for fp in self.fsdp_params], slot)
+        # the all-gather output of this group has the reduce-scatter input's layout (rank r's
+        # padded shards at r * row_bytes), so a parameter lands at its gradient's offset
+        slot.push = self.gather.target if (self.gather is not None and esize == self.gather.esize) else None
+        try:
+            self.ctx.optimizer.step_from_peers([fp.sharded_param for fp in self.fsdp_params], slot)
+        finally:
+            pushed, slot.push = slot.push is not None, None
+        if self.gather is not None:
+            if pushed:
+                self.gather.mark_pushed()
+            else:
+                self.gather.invalidate()
         self.ctx.fused_calls += 1
         return None
 
@@ -157,9 +178,65 @@ class PeerAllGather(AllGather):  # type: ignore[misc,valid-type]
         return None
 
 
+class PushedAllGather(AllGather):  # type: ignore[misc,valid-type]
+    """FSDP2's parameter all-gather of one group, served by the step kernel's pushes.
+
+    The group's all-gather output lives in one persistent symmetric buffer.  While it is
+    *current* (the last change of the group's sharded parameters was a fused update that
+    pushed them, on every rank) an all-gather only enqueues a bounded wait for the ranks'
+    "pushed" flags; otherwise (first use, after a checkpoint load, after an update that did
+    not go through the fused kernel) it is an NCCL all-gather into the same buffer.  The
+    sharded tensors' version counters reveal in-place changes made by anything else.
+    Every rank must reach the same verdict, which holds when all ranks run the same program.
+    """
+
+    def __init__(self, ctx: "FusedFSDPState", rs: FusedReduceScatter) -> None:
+        self.ctx = ctx
+        self.rs = rs
+        self.esize = torch.empty((), dtype=rs.dtype).element_size()
+        self.numel = rs.input_numel
+        self.supported = rs.supported
+        self.target: Optional[ParamPush] = None
+        if self.supported:
+            buf = ctx.peers.allocate(self.numel * self.esize)
+            self.target = ParamPush(buf, ctx.peers.new_channel())
+        self._current = False
+        self._versions: list[int] = []
+
+    def _param_versions(self) -> list[int]:
+        return [local_tensor(fp.sharded_param)._version for fp in self.rs.fsdp_params]
+
+    def mark_pushed(self) -> None:
+        self._current = True
+        self._versions = self._param_versions()
+
+    def invalidate(self) -> None:
+        self._current = False
+
+    def is_current(self) -> bool:
+        return self._current and self._versions == self._param_versions()
+
+    def allocate(self, size, *, dtype, device):
+        if self.target is not None and int(size[0]) == self.numel and dtype == self.rs.dtype:
+            return self.target.buf.view(0, self.numel, dtype)
+        return torch.empty(*size, dtype=dtype, device=device)
+
+    def __call__(self, output_tensor, input_tensor, group, async_op=False):
+        t = self.target
+        mine = t is not None and output_tensor.data_ptr() == t.buf.tensor.data_ptr() and not async_op
+        if mine and self.is_current():
+            peers = self.ctx.peers
+            args = peers.comm_args(t.buf, t.epoch, t.channel, t.channel)
+            peers.wait(args, t.channel)
+            self.ctx.ag_eliminated += 1
+            return None
+        self.ctx.ag_fallbacks += 1
+        return dist.all_gather_into_tensor(output_tensor, input_tensor, group=group, async_op=async_op)
+
+
 class FusedFSDPState:
     def __init__(self, model: nn.Module, optimizer: FlashOptimizer, group, timeout_s, use_multicast, depth,
-                 max_ctas=0, own_all_gather=False):
+                 max_ctas=0, own_all_gather=False, push_params=False):
         self.optimizer = optimizer
         modules = [m for m in model.modules() if FSDPModule is not None and isinstance(m, FSDPModule)]
         if not modules:
@@ -188,6 +265,27 @@ class FusedFSDPState:
             m.set_custom_reduce_scatter(comm)
         self.ag_calls = 0
         self.ag_fallbacks = 0
+        self.ag_eliminated = 0
+        self.gathers: list[PushedAllGather] = []
+        if push_params:
+            if own_all_gather:
+                raise ValueError("push_params and own_all_gather are alternatives")
+            by_param = {}
+            for m, comm in self.comms:
+                gather = PushedAllGather(self, comm)
+                comm.gather = gather
+                self.gathers.append(gather)
+                m.set_custom_all_gather(gather)
+                for fp in comm.fsdp_params:
+                    by_param[id(fp.sharded_param)] = gather
+
+            def on_local_update(params, _by_param=by_param):
+                for p in params:
+                    g = _by_param.get(id(p))
+                    if g is not None:
+                        g.invalidate()
+
+            optimizer._local_update_listeners.append(on_local_update)
         if own_all_gather:
             # the all-gather output of a group is as large as its reduce-scatter input;
             # three buffers: one being copied out, one prefetched, one spare
@@ -210,6 +308,7 @@ def enable_fused_fsdp(
     depth: int = 2,
     max_ctas: int = 0,
     own_all_gather: bool = False,
+    push_params: bool = False,
 ) -> Optional[FusedFSDPState]:
     """Fuse FSDP2's gradient reduce-scatter with ``optimizer``'s sharded update.
 
@@ -225,7 +324,12 @@ def enable_fused_fsdp(
     of the inbound traffic of peer loads) instead of ``world`` peer loads summed in fp32.
     ``own_all_gather`` also replaces FSDP2's parameter all-gather by this library's
     pull kernel over symmetric buffers (:class:`PeerAllGather`).
+    ``push_params`` instead removes that all-gather: the update kernel stores the new
+    parameters into every rank's all-gather buffer (:class:`PushedAllGather`); costs one
+    unsharded copy of the parameters per rank (``.ag_eliminated`` counts the all-gathers
+    that moved no data).
     """
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return None
-    return FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas, own_all_gather)
+    return FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas, own_all_gather,
+                          push_params)

@@ -11,6 +11,10 @@ library's kernels).  It owns
 * a 4-word local *status* tensor where a kernel records a wait that ran out;
 * any number of :class:`SymmBuffer` allocations.
 
+A step kernel can also push the parameters it has just updated into a second
+symmetric buffer of every rank (:class:`ParamPush`), publishing a third flag
+("pushed") when done: the all-gather of the next forward pass then only waits.
+
 Ordering protocol for a buffer with channels (ready, done) and epoch ``e``:
 a consumer kernel publishes ``ready = e`` ("my copy of the buffer is written",
 true by stream order), waits until every rank has published it, reads all
@@ -33,7 +37,7 @@ import torch.distributed as dist
 
 from ..ops import native
 
-CHANNELS = 64
+CHANNELS = 256
 
 
 class CommTimeoutError(RuntimeError):
@@ -103,6 +107,14 @@ class PeerGroup:
             dist.barrier(group=self.group)
         return buf
 
+    def new_channel(self) -> int:
+        """One fresh channel; same sequence on every rank."""
+        if self._next_channel + 1 > CHANNELS:
+            raise RuntimeError("out of signal channels")
+        c = self._next_channel
+        self._next_channel += 1
+        return c
+
     def new_channels(self) -> tuple[int, int]:
         """A fresh (ready, done) channel pair; same sequence on every rank."""
         if self._next_channel + 2 > CHANNELS:
@@ -169,6 +181,18 @@ class PeerGroup:
 
 
 @dataclass
+class ParamPush:
+    """Target of the step kernels' all-gather on write: every rank's copy of ``buf`` receives
+    the updated parameters at (gradient byte offset + ``delta``); ``epoch`` counts the
+    launches that pushed and is what the ``channel`` flags carry."""
+
+    buf: SymmBuffer
+    channel: int
+    delta: int = 0
+    epoch: int = 0
+
+
+@dataclass
 class PeerGradients:
     """What an optimizer needs to step straight from the ranks' symmetric gradient buffers."""
 
@@ -182,12 +206,24 @@ class PeerGradients:
     grad_out_sub: int = 0
     key: int = 0
     epoch: int = 0  # last epoch used on this buffer
+    push: Optional[ParamPush] = None  # step kernels also send the new parameters there
 
     def next_args(self) -> native.FoCommArgs:
         self.epoch += 1
-        return self.group.comm_args(
+        a = self.group.comm_args(
             self.buf, self.epoch, self.ready_channel, self.done_channel, self.grad_out, self.grad_out_sub
         )
+        if self.push is not None:
+            t = self.push
+            t.epoch += 1
+            a.push = 1
+            for r in range(a.world):
+                a.param_out[r] = t.buf.ptrs[r]
+            a.param_out_mc = t.buf.multicast_ptr if (a.multicast and t.buf.multicast_ptr) else None
+            a.param_out_delta = t.delta
+            a.push_epoch = t.epoch & 0xFFFFFFFF
+            a.pushed_channel = t.channel
+        return a
 
     def wait_done(self) -> None:
         """Current stream waits until every rank has finished reading the buffer's last use."""

@@ -223,3 +223,84 @@ def _fsdp_worker(rank, world):
 
 def test_fused_fsdp_matches_nccl_fsdp():
     run_distributed(_fsdp_worker, world_size=2, backend="nccl")
+
+
+def _fsdp_push_worker(rank, world):
+    from torch.distributed.fsdp import fully_shard
+
+    from flashoptim_b200 import FlashAdamW, enable_gradient_release
+    from flashoptim_b200.parallel import enable_fused_fsdp
+
+    dev = torch.device("cuda", rank)
+    errors = []
+
+    def shard(m):
+        for layer in m:
+            if isinstance(layer, nn.Linear):
+                fully_shard(layer)
+        fully_shard(m)
+        return m
+
+    for release in (False, True):
+        plain, fused = shard(_net(dev)), shard(_net(dev))
+        o1 = FlashAdamW(plain.parameters(), lr=5e-4, weight_decay=1e-2)
+        o2 = FlashAdamW(fused.parameters(), lr=5e-4, weight_decay=1e-2)
+        state = enable_fused_fsdp(fused, o2, push_params=True)
+        if release:
+            enable_gradient_release(plain, o1)
+            enable_gradient_release(fused, o2)
+        tol = get_tolerances(torch.bfloat16, True)
+        for step, (x, y) in enumerate(_batches(world)):
+            xs = x[rank * 8:(rank + 1) * 8].to(dev, torch.bfloat16)
+            ys = y[rank * 8:(rank + 1) * 8].to(dev)
+            losses = []
+            for model, opt in ((plain, o1), (fused, o2)):
+                loss = nn.functional.cross_entropy(model(xs).float(), ys)
+                loss.backward()
+                losses.append(float(loss))
+                if not release:
+                    opt.step()
+                    opt.zero_grad()
+            state.check()
+            if abs(losses[0] - losses[1]) > 2e-2 * max(1.0, abs(losses[0])):
+                errors.append(f"release={release} step {step}: loss {losses[1]} vs {losses[0]}")
+            for (n1, p1), (_, p2) in zip(plain.named_parameters(), fused.named_parameters()):
+                errors += check_similar(p2.detach().full_tensor(), p1.detach().full_tensor(), tol,
+                                        f"push release={release} step {step} {n1}")
+            # what the next all-gathers hand to FSDP2: every rank's shards, bit for bit
+            for gi, gather in enumerate(state.gathers):
+                if not gather.is_current():
+                    errors.append(f"release={release} step {step}: group {gi} was not pushed")
+                    continue
+                t = gather.target
+                state.peers.wait(state.peers.comm_args(t.buf, t.epoch, t.channel, t.channel), t.channel)
+                mine = torch.cat([fp._sharded_param_data.view(-1) for fp in gather.rs.fsdp_params])
+                want = torch.empty(world * mine.numel(), dtype=mine.dtype, device=dev)
+                dist.all_gather_into_tensor(want, mine)
+                got = t.buf.view(0, want.numel(), want.dtype)
+                if not torch.equal(got.view(torch.int16), want.view(torch.int16)):
+                    bad = int((got.view(torch.int16) != want.view(torch.int16)).sum())
+                    errors.append(f"release={release} step {step}: group {gi}: {bad} pushed elements differ")
+            state.check()
+        if state.fallbacks or state.ag_eliminated < 8:
+            errors.append(f"release={release}: rs fallbacks {state.fallbacks}, all-gathers without data movement "
+                          f"{state.ag_eliminated}, with NCCL {state.ag_fallbacks}")
+        # a local update (no push) must send the next all-gather back to NCCL
+        before = state.ag_fallbacks
+        if not release:
+            for p in fused.parameters():
+                p.grad = torch.zeros_like(p)
+            o2.step()
+            o2.zero_grad()
+            if any(g.is_current() for g in state.gathers):
+                errors.append("a local step left pushed parameters marked current")
+            with torch.no_grad():
+                fused(xs)
+            if state.ag_fallbacks == before:
+                errors.append("all-gather after a local step did not move data")
+            state.check()
+    return errors
+
+
+def test_fused_fsdp_param_push_replaces_all_gather():
+    run_distributed(_fsdp_push_worker, world_size=2, backend="nccl")

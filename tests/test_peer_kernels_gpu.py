@@ -94,9 +94,28 @@ def test_peer_adam_matches_local_step_on_mean_gradient(world, layout):
                          [s[3] for s in new], [s[4] for s in new], [s[5] for s in new])
         rows[:, 1] = offs
         h.grad_scale = 1.0 / world
+        # all-gather on write: the new parameters also go to every rank's parameter buffer
+        # (same layout as the gradient rows), and channel 2 reports it with its own epoch
+        pushed = [torch.zeros(nbytes, dtype=torch.uint8, device=DEV) for _ in range(world)]
+        args.push = 1
+        for q in range(world):
+            args.param_out[q] = pushed[q].data_ptr()
+        args.param_out_delta = 0
+        args.push_epoch = 9
+        args.pushed_channel = 2
         launch_adam_peer(SegmentTable(torch.device(DEV, torch.cuda.current_device())), rows, torch.bfloat16, 1,
                          True, h, args)
         g.check_status()
+        for q in range(world):
+            assert int(pads[q][2 * 8 + r]) == 9
+            for st, n, off in zip(new, sizes, offs):
+                got = pushed[q][off:off + 2 * n].view(torch.bfloat16)
+                assert torch.equal(got.view(torch.int16), st[0].view(torch.int16)), (r, q, n)
+            # nothing outside this rank's segments was written
+            mask = torch.ones(nbytes, dtype=torch.bool, device=DEV)
+            for n, off in zip(sizes, offs):
+                mask[off:off + 2 * n] = False
+            assert int(pushed[q][mask].count_nonzero()) == 0
         for i, (st, (pn, mn, vn), g32) in enumerate(zip(new, want, grads)):
             rec = oracle.ecc_decode_ref(st[0].cpu(), st[1].cpu())
             half_ulp = torch.exp2(oracle.ecc_log_scale(st[0].cpu()).float())
