@@ -57,9 +57,10 @@ def parse_args():
     ap.add_argument("--comm-ctas", type=int, default=0, help="grid cap of the fused reduce-scatter kernel")
     ap.add_argument("--own-all-gather", action="store_true",
                     help="fused path: FSDP2's parameter all-gather through this library's pull kernel")
-    ap.add_argument("--push-params", action="store_true",
+    ap.add_argument("--push-params", default="auto", choices=["auto", "on", "off"],
                     help="fused path: the update kernel also stores the new parameters into every rank's "
-                         "all-gather buffer, so FSDP2's parameter all-gathers move no data")
+                         "all-gather buffer, so FSDP2's parameter all-gathers move no data; auto = on at "
+                         "2 GPUs (the size it has been measured at), off otherwise")
     ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
                     help="fused path: NVSwitch multimem.ld_reduce (on) or peer loads summed in fp32 (off); "
                          "auto = peer loads up to 4 GPUs, multimem above (the faster one in the "
@@ -229,13 +230,16 @@ def main():
     use_multicast = (world > 4) if args.multicast == "auto" else args.multicast == "on"
     if args.no_multicast:
         use_multicast = False
+    push_params = (world == 2) if args.push_params == "auto" else args.push_params == "on"
+    if args.own_all_gather:
+        push_params = False
     if args.impl == "ours" and args.fused_comm == "auto":
         try:
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
             fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=60.0, max_ctas=args.comm_ctas,
                                                     use_multicast=use_multicast, own_all_gather=args.own_all_gather,
-                                                    push_params=args.push_params)
+                                                    push_params=push_params)
             fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
             if rank == 0:
@@ -359,7 +363,7 @@ def main():
                 "optimizer": f"{'FlashLion' if args.optimizer == 'lion' else 'FlashAdamW'} mwb={mwb}",
                 "gradient_release": bool(args.gradient_release), "fused_comm": bool(fused_comm),
                 "fused_comm_multicast": bool(fused_comm and use_multicast),
-                "fused_param_push": bool(fused_comm and args.push_params),
+                "fused_param_push": bool(fused_comm and push_params),
                 "activation_checkpointing": bool(cfg.activation_checkpointing),
                 "l2": "working set (>= 16 GB of weights) far exceeds the 126 MB L2; no flush",
             },
