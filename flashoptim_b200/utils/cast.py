@@ -91,27 +91,40 @@ def cast_model(
 
     name_of_param = {p: n for n, p in model.named_parameters()}
     name_of_buffer = {b: n for n, b in model.named_buffers()}
-    converted: dict[int, torch.Tensor] = {}  # storage address -> cast tensor (keeps ties)
 
-    def convert(t: torch.Tensor) -> torch.Tensor:
-        # tensors without storage (meta device) all report address 0: key those by identity,
-        # which still keeps parameters tied through one Parameter object tied
-        key = t.data.data_ptr() if t.device.type != "meta" else -id(t)
-        if key not in converted:
-            converted[key] = t.data.to(dtype=dtype)
-        return converted[key]
+    # Tensors that alias each other (tied weights: one Parameter reachable from two modules,
+    # or two Parameters over one storage) are found BEFORE anything is converted, while every
+    # storage is still alive and an address therefore identifies it.  Looking addresses up
+    # during the conversion would not be safe: a converted tensor may be placed where an
+    # already released fp32 tensor used to live.  (The reference keys a map by ``data_ptr()``
+    # while it converts, ``flashoptim/optimizers.py:2145-2185``.)
+    aliases: dict[Any, list[torch.Tensor]] = {}
+    visited: set[int] = set()
+
+    def collect(t: torch.Tensor) -> None:
+        if id(t) in visited:
+            return
+        visited.add(id(t))
+        if t.device.type == "meta" or t.numel() == 0:
+            key: Any = ("object", id(t))  # no storage to compare
+        else:
+            key = (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype, str(t.device))
+        aliases.setdefault(key, []).append(t)
 
     for module in model.modules():
         if selective and isinstance(module, _STATEFUL_NORMS):
             continue
         for param in module.parameters(recurse=False):
-            if name_of_param.get(param, "") in fp32_params:
-                continue
-            param.data = convert(param)
+            if name_of_param.get(param, "") not in fp32_params:
+                collect(param)
         for buf in module.buffers(recurse=False):
-            if name_of_buffer.get(buf, "") in fp32_buffers or not buf.is_floating_point():
-                continue
-            buf.data = convert(buf)
+            if name_of_buffer.get(buf, "") not in fp32_buffers and buf.is_floating_point():
+                collect(buf)
+
+    for group in aliases.values():
+        cast = group[0].data.to(dtype=dtype)
+        for t in group:
+            t.data = cast
 
     if specs:
         for name, module in model.named_modules():

@@ -123,3 +123,47 @@ def test_meta_device_parameters_are_not_merged():
     cast_model(m)
     assert m[0].weight.shape == (8, 4) and m[1].weight.shape == (2, 8)
     assert m[0].weight.dtype == torch.bfloat16 and m[0].weight.device.type == "meta"
+
+
+def test_parameter_shared_by_two_modules_is_converted_once():
+    """One Parameter object registered in two modules (how Hugging Face ties an output
+    bias) is visited twice; the second visit must not pick up some other tensor that
+    happens to live where a released fp32 tensor used to be."""
+
+    class Owner(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.bias = nn.Parameter(torch.randn(32))  # 64 bytes once narrowed ...
+
+    class Head(nn.Module):
+        def __init__(self, bias):
+            super().__init__()
+            self.decoder = nn.Linear(16, 32, bias=False)
+            self.decoder.bias = bias  # same Parameter object as the owner's
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            # ... the size of the fp32 biases released just before it is converted
+            self.body = nn.ModuleList([nn.Linear(16, 16) for _ in range(64)])
+            self.owner = Owner()
+            self.head = Head(self.owner.bias)
+
+    for seed in range(5):
+        torch.manual_seed(seed)
+        m = Net()
+        want = {n: p.detach().to(torch.bfloat16) for n, p in m.named_parameters(remove_duplicate=False)}
+        cast_model(m, torch.bfloat16)
+        assert m.head.decoder.bias is m.owner.bias
+        for n, p in m.named_parameters(remove_duplicate=False):
+            assert p.shape == want[n].shape and torch.equal(p, want[n]), n
+
+
+def test_views_of_one_storage_with_different_shapes_are_cast_separately():
+    m = nn.Module()
+    base = torch.randn(4, 4)
+    m.a = nn.Parameter(base)
+    m.b = nn.Parameter(base.view(16))  # same address, other shape: not a tie cast_model can keep
+    cast_model(m, torch.bfloat16)
+    assert m.a.shape == (4, 4) and m.b.shape == (16,)
+    assert torch.equal(m.a.view(16), m.b)
