@@ -1,0 +1,74 @@
+"""Host-side bookkeeping of the all-gather on write (no GPU, no process group): when may
+FSDP2's all-gather be replaced by a flag wait, and what sends it back to NCCL."""
+
+from types import SimpleNamespace
+
+import torch
+
+from flashoptim_b200.parallel.fsdp import PushedAllGather
+from flashoptim_b200.parallel.symm import ParamPush, PeerGradients
+
+
+def _gather(n_params=3):
+    params = [SimpleNamespace(sharded_param=torch.zeros(8, dtype=torch.bfloat16)) for _ in range(n_params)]
+    rs = SimpleNamespace(dtype=torch.bfloat16, input_numel=2 * 8 * n_params, supported=False, fsdp_params=params)
+    return PushedAllGather(SimpleNamespace(), rs), params
+
+
+def test_not_current_until_a_push_and_after_invalidate():
+    g, _ = _gather()
+    assert not g.is_current()
+    g.mark_pushed()
+    assert g.is_current()
+    g.invalidate()
+    assert not g.is_current()
+
+
+def test_in_place_change_of_a_shard_is_noticed():
+    g, params = _gather()
+    g.mark_pushed()
+    params[1].sharded_param.add_(1)  # e.g. a checkpoint load or an fp32 import
+    assert not g.is_current()
+    g.mark_pushed()
+    assert g.is_current()
+    params[2].sharded_param.copy_(torch.ones(8))
+    assert not g.is_current()
+
+
+def test_reads_do_not_invalidate():
+    g, params = _gather()
+    g.mark_pushed()
+    _ = params[0].sharded_param.float().sum() + params[0].sharded_param.view(-1)[0]
+    assert g.is_current()
+
+
+def test_unsupported_group_allocates_ordinary_memory():
+    g, _ = _gather()
+    assert g.target is None
+    out = g.allocate((48,), dtype=torch.bfloat16, device=torch.device("cpu"))
+    assert out.shape == (48,) and out.dtype == torch.bfloat16
+
+
+def test_push_epoch_counts_launches_and_fills_the_kernel_arguments():
+    from flashoptim_b200.ops import native
+
+    class FakeGroup:
+        world, rank = 2, 1
+
+        def comm_args(self, buf, epoch, ready, done, grad_out=None, grad_out_sub=0):
+            a = native.FoCommArgs()
+            a.world, a.rank, a.epoch = self.world, self.rank, epoch
+            return a
+
+    buf = SimpleNamespace(ptrs=[4096, 8192], multicast_ptr=0)
+    push = ParamPush(buf, channel=7, delta=64)
+    pg = PeerGradients(FakeGroup(), buf, 0, 1)
+    a = pg.next_args()
+    assert a.push == 0  # nothing asked for
+    pg.push = push
+    a = pg.next_args()
+    b = pg.next_args()
+    assert (a.push, a.push_epoch, b.push_epoch, push.epoch) == (1, 1, 2, 2)
+    assert (a.epoch, b.epoch) == (2, 3)
+    assert [a.param_out[0], a.param_out[1]] == [4096, 8192] and not a.param_out_mc
+    assert a.param_out_delta == 64 and a.pushed_channel == 7
