@@ -68,9 +68,10 @@ class _Pool:
 
 
 class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
-    def __init__(self, ctx: "FusedFSDPState", fsdp_params: list) -> None:
+    def __init__(self, ctx: "FusedFSDPState", fsdp_params: list, param_group=None) -> None:
         self.ctx = ctx
         self.fsdp_params = fsdp_params
+        self.param_group = param_group  # FSDP2's group object (for settings that can change later)
         self._slot: Optional[PeerGradients] = None
         self.gather: Optional["PushedAllGather"] = None  # receives the updated parameters
         w = ctx.peers.world
@@ -89,7 +90,9 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
     def allocate(self, size, *, dtype, device):
         numel = int(size[0])
         esize = torch.empty((), dtype=dtype).element_size()
-        if (self.supported and numel == self.input_numel and dtype == self.dtype
+        # a user's all-reduce hook post-processes the reduce-scatter output: the update must wait for it
+        hooked = getattr(self.param_group, "_all_reduce_hook", None) is not None
+        if (self.supported and not hooked and numel == self.input_numel and dtype == self.dtype
                 and numel * esize <= self.ctx.pool_bytes):
             slot = self.ctx.pool.take()
             slot.wait_done()  # every rank is done reading this buffer's previous contents
@@ -248,6 +251,11 @@ class FusedFSDPState:
                 groups.append((m, pg))
         if not groups:
             raise ValueError("no FSDP parameter groups found")
+        if any(getattr(pg, "_is_hsdp", False) for _, pg in groups):
+            # FSDP2 all-reduces the reduce-scatter output across replicas afterwards; an update
+            # inside the reduce-scatter would use a gradient that is averaged over one replica only
+            raise ValueError("the fused FSDP2 path does not support HSDP (replicate x shard) meshes; "
+                             "use fully_shard with optimizer.step() there")
         mesh_group = groups[0][1]._reduce_scatter_process_group
         self.peers = PeerGroup(group or mesh_group, device=groups[0][1].device, timeout_s=timeout_s,
                                use_multicast=use_multicast, max_ctas=max_ctas)
@@ -256,7 +264,7 @@ class FusedFSDPState:
         self.comms = []
         need = 0
         for m, pg in groups:
-            comm = FusedReduceScatter(self, list(pg.fsdp_params))
+            comm = FusedReduceScatter(self, list(pg.fsdp_params), pg)
             need = max(need, comm.input_numel * torch.empty((), dtype=comm.dtype).element_size())
             self.comms.append((m, comm))
         self.pool_bytes = need

@@ -175,3 +175,63 @@ def test_fsdp2_nccl_two_gpus():
 def test_fsdp2_dcp_nccl_two_gpus():
     with tempfile.TemporaryDirectory() as d:
         run_distributed(_dcp_worker, world_size=2, backend="nccl", args=(True, d))
+
+
+def _hsdp_worker(rank, world):
+    """Two-dimensional (replicate x shard) meshes: state is shard-shaped, training matches a
+    single process, state_dict wraps over both mesh dimensions, and the fused path refuses."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    from flashoptim_b200.parallel import enable_fused_fsdp
+
+    errors = []
+    device = torch.device("cpu")
+    g = torch.Generator().manual_seed(7)
+    data = [(torch.randn(world * 8, 10, generator=g), torch.randint(0, 6, (world * 8,), generator=g))
+            for _ in range(4)]
+    for shape in ((1, world), (world, 1)):
+        mesh = init_device_mesh("cpu", shape, mesh_dim_names=("replicate", "shard"))
+        for dtype, mwb, quantize in CONFIGS[:2]:
+            tag = f"hsdp {shape} {dtype} mwb={mwb}"
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                single, sharded = _net(dtype, device), _net(dtype, device)
+                for layer in sharded:
+                    if isinstance(layer, nn.Linear):
+                        fully_shard(layer, mesh=mesh)
+                fully_shard(sharded, mesh=mesh)
+                o1 = FlashAdamW(single.parameters(), lr=5e-4, master_weight_bits=mwb, quantize=quantize)
+                o2 = FlashAdamW(sharded.parameters(), lr=5e-4, master_weight_bits=mwb, quantize=quantize)
+            tol = get_tolerances(dtype, quantize)
+            for step, (x, y) in enumerate(data):
+                x = x.to(dtype)
+                xs, ys = x[rank * 8:(rank + 1) * 8], y[rank * 8:(rank + 1) * 8]
+                nn.functional.cross_entropy(single(x).float(), y).backward()
+                o1.step(); o1.zero_grad()
+                nn.functional.cross_entropy(sharded(xs).float(), ys).backward()
+                o2.step(); o2.zero_grad()
+                for (n1, p1), (_, p2) in zip(single.named_parameters(), sharded.named_parameters()):
+                    errors += check_similar(_full(p2.detach()), p1.detach(), tol, f"{tag} step {step} {n1}")
+            for p in sharded.parameters():
+                if o2.state[p]["exp_avg"].shape != tuple(p.to_local().shape):
+                    errors.append(f"{tag}: state is not shard-shaped")
+            sd = o2.state_dict()
+            for st in sd["state"].values():
+                for k, v in st.items():
+                    if k != "step" and v.dim() >= 1 and not hasattr(v, "device_mesh"):
+                        errors.append(f"{tag}: checkpoint entry {k} is not a DTensor")
+                    elif k != "step" and v.dim() >= 1 and v.device_mesh.ndim != 2:
+                        errors.append(f"{tag}: checkpoint entry {k} lost a mesh dimension")
+            o3 = FlashAdamW(sharded.parameters(), lr=5e-4, master_weight_bits=mwb, quantize=quantize)
+            o3.load_state_dict(sd)
+            try:
+                enable_fused_fsdp(sharded, o2)
+                errors.append(f"{tag}: the fused path accepted an HSDP mesh")
+            except ValueError:
+                pass
+    return errors
+
+
+def test_hsdp_mesh_gloo_two_ranks():
+    run_distributed(_hsdp_worker, world_size=2, backend="gloo")
