@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from ctypes import POINTER, Structure, c_float, c_int, c_int32, c_int64, c_void_p
+from ctypes import POINTER, Structure, c_float, c_int, c_int64, c_void_p
 from typing import Optional
 
 import torch

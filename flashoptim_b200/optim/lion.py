@@ -7,7 +7,7 @@ from typing import Any, Iterable, Literal, Optional
 
 import torch
 
-from ..ops import native, oracle
+from ..ops import oracle
 from ..ops.step import MomentumHyper, launch_momentum, launch_momentum_peer
 from ._common import err_bytes_of, pack_rows, state_mode, write_back
 from .base import FlashOptimizer

@@ -2,7 +2,6 @@
 two ranks against a single-process run on the concatenated batch, weights compared every
 step and bit-equality across ranks.  CPU ranks over gloo; the same body on two GPUs over NCCL."""
 
-import copy
 import warnings
 
 import pytest

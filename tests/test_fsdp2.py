@@ -3,7 +3,6 @@ training against a single-process run, gradient release, fp32 export, and
 ``torch.distributed.checkpoint`` round trips.  CPU ranks over gloo; the same body on two
 GPUs over NCCL."""
 
-import copy
 import os
 import tempfile
 import warnings

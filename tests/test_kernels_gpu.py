@@ -1,6 +1,5 @@
 """sm_100a kernels against the PyTorch fp32 formulation of the same operations."""
 
-import numpy as np
 import pytest
 import torch
 

@@ -2,9 +2,6 @@
 the fused FSDP2 reduce-scatter against their NCCL counterparts.  Workers never fault a
 GPU: every device-side wait is bounded and reported through a status word."""
 
-import copy
-import warnings
-
 import pytest
 import torch
 import torch.distributed as dist
@@ -32,9 +29,7 @@ def _batches(world, d=64, steps=5):
 
 
 def _peer_kernel_worker(rank, world, use_multicast):
-    import ctypes
-
-    from flashoptim_b200.ops import native, oracle
+    from flashoptim_b200.ops import oracle
     from flashoptim_b200.ops.quant import compute_ecc_bits, quantize
     from flashoptim_b200.ops.step import AdamHyper, SegmentTable, launch_adam_peer, make_rows
     from flashoptim_b200.parallel.symm import PeerGradients, PeerGroup

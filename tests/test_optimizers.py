@@ -2,7 +2,6 @@
 modelled on the reference's ``test/test_optimizers.py``."""
 
 import copy
-import math
 import warnings
 
 import pytest
@@ -16,7 +15,7 @@ from flashoptim_b200 import (
 )
 from flashoptim_b200.optim.state import MaybeQuantizedTensor
 
-from helpers import check_similar, cossim, get_tolerances, nmse
+from helpers import cossim, nmse
 from reference_optimizers import ReferenceAdamW, ReferenceLion, ReferenceSGD
 
 DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]

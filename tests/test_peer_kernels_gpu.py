@@ -6,14 +6,13 @@ out, report through the status word and leave the context usable."""
 
 import ctypes
 
-import numpy as np
 import pytest
 import torch
 
 from flashoptim_b200.ops import native, oracle
 from flashoptim_b200.ops.quant import compute_ecc_bits, quantize
 from flashoptim_b200.ops.step import (
-    AdamHyper, MomentumHyper, SegmentTable, launch_adam, launch_adam_peer, launch_momentum_peer, make_rows,
+    AdamHyper, MomentumHyper, SegmentTable, launch_adam_peer, launch_momentum_peer, make_rows,
 )
 from flashoptim_b200.parallel.symm import CommTimeoutError, PeerGroup, SymmBuffer
 

@@ -5,13 +5,12 @@ default flavours, disk round trip, pickling (modelled on the reference's
 import copy
 import io
 import pickle
-import warnings
 
 import pytest
 import torch
 import torch.nn as nn
 
-from flashoptim_b200 import FlashAdamW, FlashLion, FlashSGD, cast_model
+from flashoptim_b200 import FlashAdamW, FlashLion, FlashSGD
 from flashoptim_b200.optim.state import MaybeQuantizedTensor
 
 from test_optimizers import DEVICES, _data, _model
