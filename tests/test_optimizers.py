@@ -489,3 +489,44 @@ def test_step_with_explicit_gradients_equals_step(name):
         o2.zero_grad()
     for a, b in zip(m1.parameters(), m2.parameters()):
         assert torch.equal(a, b)
+
+
+# ---------------------------------------------------------------- memory accounting
+
+
+def _state_bytes(opt):
+    total = 0
+    for st in opt.state.values():
+        for v in st.values():
+            if isinstance(v, MaybeQuantizedTensor):
+                parts = [v.quantized, v.scales] if v.is_quantized() else [v.data]
+            elif isinstance(v, torch.Tensor) and v.dim() > 0:
+                parts = [v]
+            else:
+                parts = []
+            total += sum(t.numel() * t.element_size() for t in parts)
+    return total
+
+
+@pytest.mark.parametrize("cls,kw,mwb,quantize,want", [
+    # int8 correction + two moments of (1 byte + one fp16 scale per 32 elements)
+    (FlashAdamW, {}, 24, True, 1 + 2 * (1 + 2 / 32)),
+    (FlashAdamW, {}, 32, True, 2 + 2 * (1 + 2 / 32)),
+    (FlashAdamW, {}, None, True, 2 * (1 + 2 / 32)),
+    (FlashAdamW, {}, 24, False, 1 + 2 * 2),        # bf16 moments
+    (FlashLion, {}, 24, True, 1 + (1 + 2 / 32)),
+    (FlashSGDW, {"momentum": 0.9}, 24, True, 1 + (1 + 2 / 32)),
+    (FlashSGDW, {}, 24, True, 1.0),                # momentum-free SGD keeps no moment
+])
+def test_optimizer_state_bytes_per_parameter(cls, kw, mwb, quantize, want):
+    """The memory the states take is what the format promises: 3.125 bytes per bf16 parameter
+    for AdamW with 24-bit masters (a conventional mixed-precision AdamW keeps 12: fp32 master
+    weights and two fp32 moments), 2.06 for Lion."""
+    n = 1 << 14
+    p = nn.Parameter(torch.randn(n).to(torch.bfloat16))
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        opt = cls([p], lr=1e-3, master_weight_bits=mwb, quantize=quantize, **kw)
+    p.grad = torch.randn(n).to(torch.bfloat16) * 1e-2
+    opt.step()
+    assert _state_bytes(opt) / n == pytest.approx(want)
