@@ -67,6 +67,15 @@ class _Pool:
         return s
 
 
+def _every_rank_has_rows(sharded_param: torch.Tensor, world: int) -> bool:
+    """FSDP2 gives rank r rows [r * c, (r + 1) * c) of dimension 0 with c = ceil(rows / world);
+    a rank whose range is empty would launch fewer kernels for the group than its peers, and
+    the launches of all ranks pair up through their epochs."""
+    rows = sharded_param.shape[0] if sharded_param.dim() > 0 else 1  # DTensor: the global shape
+    chunk = -(-rows // world)
+    return (world - 1) * chunk < rows
+
+
 class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
     def __init__(self, ctx: "FusedFSDPState", fsdp_params: list, param_group=None) -> None:
         self.ctx = ctx
@@ -82,6 +91,7 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
         self.supported = all(
             fp.sharded_param.dtype == self.dtype and getattr(fp.fsdp_placement, "dim", 0) == 0
             and not fp.offload_to_cpu and id(fp.sharded_param) in owned and fp.sharded_param.requires_grad
+            and _every_rank_has_rows(fp.sharded_param, w)
             for fp in fsdp_params
         )
 

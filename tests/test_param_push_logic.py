@@ -72,3 +72,14 @@ def test_push_epoch_counts_launches_and_fills_the_kernel_arguments():
     assert (a.epoch, b.epoch) == (2, 3)
     assert [a.param_out[0], a.param_out[1]] == [4096, 8192] and not a.param_out_mc
     assert a.param_out_delta == 64 and a.pushed_channel == 7
+
+
+def test_groups_with_an_empty_shard_on_some_rank_are_left_to_nccl():
+    from flashoptim_b200.parallel.fsdp import _every_rank_has_rows
+
+    assert _every_rank_has_rows(torch.zeros(16, 4), 8)
+    assert _every_rank_has_rows(torch.zeros(9, 4), 8) is False   # chunks of 2: ranks 5..7 hold nothing
+    assert _every_rank_has_rows(torch.zeros(15, 4), 8)           # last rank holds one row
+    assert _every_rank_has_rows(torch.zeros(3), 4) is False      # chunks of 1: rank 3 is empty
+    assert _every_rank_has_rows(torch.zeros(4), 4)
+    assert _every_rank_has_rows(torch.zeros(1), 1)
