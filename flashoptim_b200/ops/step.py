@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
@@ -25,6 +26,20 @@ from . import native
 SEG_WORDS = 8  # int64 words per segment: p, g, ecc, s0, s0s, s1, s1s, n
 
 _launches = 0
+
+# FLASHOPTIM_B200_NVTX=1 brackets every fused launch with an NVTX range named after the
+# kernel family, so that a timeline shows which update (and which collective) ran where.
+_NVTX = os.environ.get("FLASHOPTIM_B200_NVTX", "0") not in ("", "0")
+
+
+def _launch(name: str, fn, *args) -> int:
+    if not _NVTX:
+        return fn(*args)
+    torch.cuda.nvtx.range_push(name)
+    try:
+        return fn(*args)
+    finally:
+        torch.cuda.nvtx.range_pop()
 
 
 def launch_count() -> int:
@@ -180,7 +195,8 @@ def launch_adam(
     segs, chunks, n_seg, total, on_dev = table.prepare(rows)
     h = hyper.to_c()
     with torch.cuda.device(table.device):
-        rc = lib.fo_adam_step(
+        rc = _launch(
+            "fo_adam_step", lib.fo_adam_step,
             segs, chunks, n_seg, total, on_dev, native.DTYPE_CODE[dtype], err_bytes, int(quantized),
             ctypes.byref(h), native.stream_ptr(table.device),
         )
@@ -205,7 +221,8 @@ def launch_momentum(
     segs, chunks, n_seg, total, on_dev = table.prepare(rows)
     h = hyper.to_c()
     with torch.cuda.device(table.device):
-        rc = lib.fo_momentum_step(
+        rc = _launch(
+            "fo_momentum_step", lib.fo_momentum_step,
             segs, chunks, n_seg, total, on_dev, native.DTYPE_CODE[dtype], err_bytes, state_mode,
             ctypes.byref(h), native.stream_ptr(table.device),
         )
@@ -231,7 +248,8 @@ def launch_adam_peer(
     segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(comm.world), force_device=True)
     h = hyper.to_c()
     with torch.cuda.device(table.device):
-        rc = lib.fo_adam_step_peer(
+        rc = _launch(
+            "fo_adam_step_peer", lib.fo_adam_step_peer,
             segs, chunks, n_seg, total, native.DTYPE_CODE[dtype], err_bytes, int(quantized),
             ctypes.byref(h), ctypes.byref(comm), native.stream_ptr(table.device),
         )
@@ -256,7 +274,8 @@ def launch_momentum_peer(
     segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(comm.world), force_device=True)
     h = hyper.to_c()
     with torch.cuda.device(table.device):
-        rc = lib.fo_momentum_step_peer(
+        rc = _launch(
+            "fo_momentum_step_peer", lib.fo_momentum_step_peer,
             segs, chunks, n_seg, total, native.DTYPE_CODE[dtype], err_bytes, state_mode,
             ctypes.byref(h), ctypes.byref(comm), native.stream_ptr(table.device),
         )
