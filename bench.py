@@ -61,6 +61,8 @@ def parse_args():
                     help="fused path: the update kernel also stores the new parameters into every rank's "
                          "all-gather buffer, so FSDP2's parameter all-gathers move no data; auto = on at "
                          "2 GPUs (the size it has been measured at), off otherwise")
+    ap.add_argument("--push-budget-gb", type=float, default=0.0,
+                    help="with the parameter push: GiB of persistent all-gather buffers per GPU (0: every group)")
     ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
                     help="fused path: NVSwitch multimem.ld_reduce (on) or peer loads summed in fp32 (off); "
                          "auto = peer loads up to 4 GPUs, multimem above (the faster one in the "
@@ -239,7 +241,8 @@ def main():
 
             fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=60.0, max_ctas=args.comm_ctas,
                                                     use_multicast=use_multicast, own_all_gather=args.own_all_gather,
-                                                    push_params=push_params)
+                                                    push_params=push_params,
+                                                    push_budget_bytes=int(args.push_budget_gb * 2**30) or None)
             fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
             if rank == 0:

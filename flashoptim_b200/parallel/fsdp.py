@@ -247,9 +247,22 @@ class PushedAllGather(AllGather):  # type: ignore[misc,valid-type]
         return dist.all_gather_into_tensor(output_tensor, input_tensor, group=group, async_op=async_op)
 
 
+def select_push_groups(sizes: list[int], budget_bytes: Optional[int]) -> list[bool]:
+    """Which groups get a persistent all-gather buffer: all supported ones (size > 0) without
+    a budget, else in module order as long as their buffers fit into ``budget_bytes`` (the
+    buffers together hold an unsharded copy of those groups' parameters on every rank)."""
+    out, used = [], 0
+    for n in sizes:
+        take = n > 0 and (budget_bytes is None or used + n <= budget_bytes)
+        if take:
+            used += n
+        out.append(take)
+    return out
+
+
 class FusedFSDPState:
     def __init__(self, model: nn.Module, optimizer: FlashOptimizer, group, timeout_s, use_multicast, depth,
-                 max_ctas=0, own_all_gather=False, push_params=False):
+                 max_ctas=0, own_all_gather=False, push_params=False, push_budget_bytes=None):
         self.optimizer = optimizer
         modules = [m for m in model.modules() if FSDPModule is not None and isinstance(m, FSDPModule)]
         if not modules:
@@ -289,7 +302,12 @@ class FusedFSDPState:
             if own_all_gather:
                 raise ValueError("push_params and own_all_gather are alternatives")
             by_param = {}
-            for m, comm in self.comms:
+            chosen = select_push_groups(
+                [comm.input_numel * torch.empty((), dtype=comm.dtype).element_size() if comm.supported else 0
+                 for _, comm in self.comms], push_budget_bytes)
+            for (m, comm), take in zip(self.comms, chosen):
+                if not take:
+                    continue  # this group keeps FSDP2's own all-gather
                 gather = PushedAllGather(self, comm)
                 comm.gather = gather
                 self.gathers.append(gather)
@@ -327,6 +345,7 @@ def enable_fused_fsdp(
     max_ctas: int = 0,
     own_all_gather: bool = False,
     push_params: bool = False,
+    push_budget_bytes: Optional[int] = None,
 ) -> Optional[FusedFSDPState]:
     """Fuse FSDP2's gradient reduce-scatter with ``optimizer``'s sharded update.
 
@@ -345,9 +364,11 @@ def enable_fused_fsdp(
     ``push_params`` instead removes that all-gather: the update kernel stores the new
     parameters into every rank's all-gather buffer (:class:`PushedAllGather`); costs one
     unsharded copy of the parameters per rank (``.ag_eliminated`` counts the all-gathers
-    that moved no data).
+    that moved no data).  ``push_budget_bytes`` bounds that copy: groups get a buffer in
+    module order while they fit, the others keep FSDP2's all-gather (Llama-3-70B's 140 GB
+    of bf16 parameters do not fit beside the training state of a 180 GB GPU).
     """
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return None
     return FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas, own_all_gather,
-                          push_params)
+                          push_params, push_budget_bytes)

@@ -83,3 +83,11 @@ def test_groups_with_an_empty_shard_on_some_rank_are_left_to_nccl():
     assert _every_rank_has_rows(torch.zeros(3), 4) is False      # chunks of 1: rank 3 is empty
     assert _every_rank_has_rows(torch.zeros(4), 4)
     assert _every_rank_has_rows(torch.zeros(1), 1)
+
+
+def test_push_budget_takes_groups_in_order_while_they_fit():
+    from flashoptim_b200.parallel.fsdp import select_push_groups
+
+    assert select_push_groups([10, 0, 20, 30], None) == [True, False, True, True]
+    assert select_push_groups([10, 20, 30, 5], 35) == [True, True, False, True]
+    assert select_push_groups([10, 20], 0) == [False, False]
