@@ -11,6 +11,8 @@ from ..ops import native
 from ..ops.quant import compute_ecc_bits
 from ..ops.step import SEG_WORDS
 
+GROUP = 32  # elements per quantisation group (one fp16 scale each)
+
 
 def write_back(
     param: torch.Tensor, p32: torch.Tensor, errors: Optional[torch.Tensor], master_bytewidth: int
@@ -33,23 +35,43 @@ def pack_rows(
 
     The gradient entry of an item is a tensor (local steps) or an ``int`` byte offset
     into the ranks' symmetric gradient buffers (steps fused with the collective).
+
+    The kernels trust this table, so every extent is checked here: a state, correction or
+    gradient tensor of the wrong length (say, from a checkpoint of another model) raises
+    instead of being read or written out of bounds.
     """
     rows = np.zeros((len(items), SEG_WORDS), dtype=np.int64)
     for i, (p, g, st) in enumerate(items):
         r = rows[i]
+        n = p.numel()
         r[0] = p.data_ptr()
-        r[1] = g if isinstance(g, int) else g.data_ptr()
+        if isinstance(g, int):
+            r[1] = g
+        else:
+            if g.numel() != n or g.dtype != p.dtype:
+                raise ValueError(f"gradient of {g.numel()} {g.dtype} elements for a parameter of {n} {p.dtype}")
+            r[1] = g.data_ptr()
         e = st.get("error_bits")
         if e is not None:
+            if e.numel() != n:
+                raise ValueError(f"error_bits holds {e.numel()} codes for a parameter of {n} elements")
             r[2] = e.data_ptr()
         for k, key in enumerate(state_keys):
             s = st[key]
             if s.is_quantized():
-                r[3 + 2 * k] = s.quantized.data_ptr()
-                r[4 + 2 * k] = s.scales.data_ptr()
+                q, sc = s.quantized, s.scales
+                if q.numel() != n or sc.numel() != (n + GROUP - 1) // GROUP:
+                    raise ValueError(
+                        f"state {key!r}: {q.numel()} codes and {sc.numel()} scales for a parameter of {n} "
+                        f"elements (expected {n} and {(n + GROUP - 1) // GROUP})")
+                r[3 + 2 * k] = q.data_ptr()
+                r[4 + 2 * k] = sc.data_ptr()
             else:
-                r[3 + 2 * k] = s.data.data_ptr()
-        r[7] = p.numel()
+                d = s.data
+                if d.numel() != n or d.dtype != p.dtype:
+                    raise ValueError(f"state {key!r}: {d.numel()} {d.dtype} elements for a parameter of {n} {p.dtype}")
+                r[3 + 2 * k] = d.data_ptr()
+        r[7] = n
     return rows
 
 

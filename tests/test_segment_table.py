@@ -27,3 +27,39 @@ def test_prefix_is_rebuilt_when_the_chunk_size_changes():
     assert total_large == 3
     *_, total_again, _ = table.prepare(rows, chunk=2048)
     assert total_again == 6
+
+
+def test_pack_rows_refuses_tensors_of_the_wrong_extent():
+    import pytest
+
+    from flashoptim_b200.optim._common import pack_rows
+    from flashoptim_b200.optim.state import MaybeQuantizedTensor
+
+    def state(n_codes, n_scales):
+        s = MaybeQuantizedTensor(torch.zeros(1), try_quantize=False)
+        s._data, s._quantized, s._scales = None, torch.zeros(n_codes, dtype=torch.int8), torch.zeros(
+            n_scales, dtype=torch.float16)
+        return s
+
+    p = torch.zeros(100, dtype=torch.bfloat16)
+    g = torch.zeros(100, dtype=torch.bfloat16)
+    good = {"exp_avg": state(100, 4), "error_bits": torch.zeros(100, dtype=torch.int8)}
+    rows = pack_rows([(p, g, good)], ("exp_avg",))
+    assert rows[0, 7] == 100 and rows[0, 0] == p.data_ptr() and rows[0, 4] == good["exp_avg"].scales.data_ptr()
+    assert pack_rows([(p, 4096, good)], ("exp_avg",))[0, 1] == 4096  # byte offset instead of a tensor
+    for bad in (
+        {"exp_avg": state(100, 3), "error_bits": good["error_bits"]},      # one scale short
+        {"exp_avg": state(96, 4), "error_bits": good["error_bits"]},       # codes of another tensor
+        {"exp_avg": good["exp_avg"], "error_bits": torch.zeros(50, dtype=torch.int8)},
+    ):
+        with pytest.raises(ValueError):
+            pack_rows([(p, g, bad)], ("exp_avg",))
+    with pytest.raises(ValueError):
+        pack_rows([(p, torch.zeros(99, dtype=torch.bfloat16), good)], ("exp_avg",))
+    with pytest.raises(ValueError):
+        pack_rows([(p, torch.zeros(100), good)], ("exp_avg",))  # fp32 gradient for a bf16 parameter
+    full = MaybeQuantizedTensor(torch.zeros(100), try_quantize=False, storage_dtype=torch.bfloat16)
+    assert pack_rows([(p, g, {"exp_avg": full})], ("exp_avg",))[0, 3] == full.data.data_ptr()
+    short = MaybeQuantizedTensor(torch.zeros(10), try_quantize=False, storage_dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        pack_rows([(p, g, {"exp_avg": short})], ("exp_avg",))
