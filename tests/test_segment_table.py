@@ -63,3 +63,52 @@ def test_pack_rows_refuses_tensors_of_the_wrong_extent():
     short = MaybeQuantizedTensor(torch.zeros(10), try_quantize=False, storage_dtype=torch.bfloat16)
     with pytest.raises(ValueError):
         pack_rows([(p, g, {"exp_avg": short})], ("exp_avg",))
+
+
+def test_every_optimizer_packs_a_consistent_table(monkeypatch):
+    """The packing that feeds the CUDA kernels, run here on CPU tensors with the launch
+    replaced by a recorder: one row per parameter, every address and length filled in, for
+    every optimizer x dtype x master-weight width x state mode."""
+    import warnings
+
+    import torch.nn as nn
+
+    import flashoptim_b200.optim.adam as adam_mod
+    import flashoptim_b200.optim.lion as lion_mod
+    import flashoptim_b200.optim.sgd as sgd_mod
+    from flashoptim_b200 import FlashAdamW, FlashLion, FlashSGD, FlashSGDW
+
+    seen = []
+
+    def record(table, rows, dtype, err, mode_or_quantized, hyper):
+        seen.append((rows.copy(), dtype, err, mode_or_quantized))
+
+    monkeypatch.setattr(adam_mod, "launch_adam", record)
+    monkeypatch.setattr(lion_mod, "launch_momentum", record)
+    monkeypatch.setattr(sgd_mod, "launch_momentum", record)
+    cases = [(FlashAdamW, {}, 2), (FlashLion, {}, 1), (FlashSGDW, {"momentum": 0.9}, 1), (FlashSGD, {}, 0)]
+    for cls, kw, n_states in cases:
+        for dtype, mwb in ((torch.bfloat16, 24), (torch.float16, 32), (torch.bfloat16, None), (torch.float32, None)):
+            for quantize in (True, False):
+                params = [nn.Parameter(torch.randn(n).to(dtype)) for n in (1, 33, 4096)]
+                with warnings.catch_warnings():
+                    warnings.simplefilter("ignore")
+                    opt = cls(params, lr=1e-3, master_weight_bits=mwb, quantize=quantize, **kw)
+                group = opt.param_groups[0]
+                items = []
+                for p in params:
+                    opt._ensure_state_initialized(p, group)
+                    items.append((p.data, torch.zeros_like(p.data), opt.state[p]))
+                seen.clear()
+                opt._pre_step_many([it[2] for it in items])
+                opt._fused_step(items, group, 0)
+                rows = np.concatenate([s[0] for s in seen])
+                assert rows.shape == (3, 8) and sorted(rows[:, 7]) == [1, 33, 4096]
+                err = {24: 1, 32: 2, None: 0}[mwb]
+                assert all(s[2] == err for s in seen)
+                assert (rows[:, 0] != 0).all() and (rows[:, 1] != 0).all()
+                assert ((rows[:, 2] != 0) == (err != 0)).all()
+                for k in range(2):
+                    has_state = k < n_states
+                    assert ((rows[:, 3 + 2 * k] != 0) == has_state).all()
+                    assert ((rows[:, 4 + 2 * k] != 0) == (has_state and quantize)).all()
