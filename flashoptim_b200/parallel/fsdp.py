@@ -292,15 +292,16 @@ class FusedFSDPState:
             self.comms.append((m, comm))
         self.pool_bytes = need
         self.pool = _Pool(self.peers, need, depth)
-        for m, comm in self.comms:
-            m.set_custom_reduce_scatter(comm)
         self.ag_calls = 0
         self.ag_fallbacks = 0
         self.ag_eliminated = 0
         self.gathers: list[PushedAllGather] = []
+        if push_params and own_all_gather:
+            raise ValueError("push_params and own_all_gather are alternatives")
+        # every symmetric allocation comes first and the communicators are installed last, so
+        # that a failed allocation leaves the model on FSDP2's own collectives
+        installs: list[tuple[nn.Module, object]] = []
         if push_params:
-            if own_all_gather:
-                raise ValueError("push_params and own_all_gather are alternatives")
             by_param = {}
             chosen = select_push_groups(
                 [comm.input_numel * torch.empty((), dtype=comm.dtype).element_size() if comm.supported else 0
@@ -311,7 +312,7 @@ class FusedFSDPState:
                 gather = PushedAllGather(self, comm)
                 comm.gather = gather
                 self.gathers.append(gather)
-                m.set_custom_all_gather(gather)
+                installs.append((m, gather))
                 for fp in comm.fsdp_params:
                     by_param[id(fp.sharded_param)] = gather
 
@@ -327,8 +328,11 @@ class FusedFSDPState:
             # three buffers: one being copied out, one prefetched, one spare
             self.ag_pool_bytes = need
             self.ag_pool = _Pool(self.peers, need, 3)
-            for m, _ in groups:
-                m.set_custom_all_gather(PeerAllGather(self))
+            installs += [(m, PeerAllGather(self)) for m, _ in groups]
+        for m, comm in self.comms:
+            m.set_custom_reduce_scatter(comm)
+        for m, gather in installs:
+            m.set_custom_all_gather(gather)
 
     def check(self) -> None:
         self.peers.check_status()
