@@ -333,6 +333,16 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
                 return group
         raise ValueError(f"Parameter {p.shape} {p.dtype} not managed by this optimizer.")
 
+    def _group_index_of_params(self) -> dict[int, int]:
+        """``id(param) -> index of its param group``, rebuilt only when the groups changed
+        (the collective-fused paths look parameters up once per bucket or FSDP group)."""
+        sig = tuple((id(g["params"]), len(g["params"])) for g in self.param_groups)
+        cache = self.__dict__.get("_index_cache")
+        if cache is None or cache[0] != sig:
+            cache = (sig, {id(p): gi for gi, g in enumerate(self.param_groups) for p in g["params"]})
+            self.__dict__["_index_cache"] = cache
+        return cache[1]
+
     def _group_index(self, group: dict[str, Any]) -> int:
         for i, g in enumerate(self.param_groups):
             if g is group:
@@ -427,7 +437,7 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         following ``step()`` / ``step_param()`` leaves it alone once.
         """
         by_group: dict[int, list[torch.Tensor]] = {}
-        index_of = {id(p): gi for gi, g in enumerate(self.param_groups) for p in g["params"]}
+        index_of = self._group_index_of_params()
         for p in params:
             by_group.setdefault(index_of[id(p)], []).append(p)
         for gi, plist in by_group.items():
@@ -453,7 +463,7 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         """Update ``params`` from explicitly given (already reduced) gradient tensors
         instead of ``.grad``, with the fused kernels on the current stream, and mark them
         so that the following ``step()`` / ``step_param()`` leaves them alone once."""
-        index_of = {id(p): gi for gi, g in enumerate(self.param_groups) for p in g["params"]}
+        index_of = self._group_index_of_params()
         by_group: dict[int, list] = {}
         for p, g in zip(params, grads):
             by_group.setdefault(index_of[id(p)], []).append((p, g))
