@@ -9,6 +9,9 @@ layer).  Rank r reduces row r of every rank and updates its shard (AdamW, 24-bit
 master weights, 8-bit states).  Timed on the device with CUDA events, max over
 ranks; every iteration touches far more than the 126 MB L2.
 
+The ``*_push`` variants also store the updated bf16 shard into every rank's parameter buffer
+(all-gather on write); compare them with ``nccl_then_step`` plus an all-gather of the shard.
+
 Roofline of the fused kernel = the slower of
   * NVLink: bytes per direction per GPU / 770 GB/s (measured peer-copy rate).  With peer
     loads a rank receives (world-1) rows of shard*2 bytes and serves as many to its
@@ -45,7 +48,7 @@ def main():
     from flashoptim_b200.ops.step import (
         AdamHyper, SegmentTable, launch_adam, launch_adam_peer, make_rows,
     )
-    from flashoptim_b200.parallel.symm import PeerGradients, PeerGroup
+    from flashoptim_b200.parallel.symm import ParamPush, PeerGradients, PeerGroup
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -78,21 +81,30 @@ def main():
         return AdamHyper(lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=1e-6, step=step,
                          decoupled=True, grad_scale=scale)
 
+    # all-gather on write: the kernel also stores its new bf16 shard into row `rank` of a second
+    # [world, shard] buffer on every rank (what FSDP2 would otherwise all-gather)
+    push_target = ParamPush(peers.allocate(n * 2), peers.new_channel())
+
     results = {}
-    for name in ("fused_peer_loads", "fused_multimem", "nccl_then_step"):
-        use_mc = name == "fused_multimem"
+    ag_out = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    for name in ("fused_peer_loads", "fused_multimem", "fused_peer_loads_push", "fused_multimem_push",
+                 "nccl_then_step", "nccl_then_step_then_all_gather"):
+        use_mc = "multimem" in name
         if use_mc and not buf.multicast_ptr:
             continue
         pg = PeerGradients(peers, buf, ready, done, grad_scale=1.0 / world)
+        pg.push = push_target if name.endswith("_push") else None
         peers.use_multicast = use_mc
         pg.epoch = results.get("_epoch", 0)
         step = [0]
 
         def run():
             step[0] += 1
-            if name == "nccl_then_step":
+            if name.startswith("nccl"):
                 dist.reduce_scatter_tensor(rs_out, grads, op=dist.ReduceOp.AVG)
                 launch_adam(table_local, rows_local, torch.bfloat16, 1, True, hyper(step[0], 1.0))
+                if name.endswith("all_gather"):
+                    dist.all_gather_into_tensor(ag_out, p)
             else:
                 launch_adam_peer(table_peer, rows_peer, torch.bfloat16, 1, True, hyper(step[0], 1.0 / world),
                                  pg.next_args())
@@ -125,9 +137,15 @@ def main():
             if name.startswith("_"):
                 continue
             rec = {"ms": round(ms_, 4)}
-            if name != "nccl_then_step":
-                inbound = shard * 2 * ((world - 1) if name == "fused_peer_loads" else (1 if world > 1 else 0))
+            if not name.startswith("nccl"):
+                inbound = shard * 2 * ((world - 1) if "peer_loads" in name else (1 if world > 1 else 0))
                 outbound = shard * 2 * (world - 1)
+                if name.endswith("_push"):
+                    # the new shard goes to the other world-1 ranks (peer stores: that many copies
+                    # leave this GPU; multimem.st: one copy leaves and the switch replicates it),
+                    # and world-1 shards arrive either way
+                    inbound += shard * 2 * (world - 1)
+                    outbound += shard * 2 * ((world - 1) if "peer_loads" in name else (1 if world > 1 else 0))
                 link_ms = max(inbound, outbound) / (link * 1e9) * 1e3
                 roof = max(link_ms, hbm_ms)
                 rec.update({"nvlink_inbound_MB": round(inbound / 1e6, 1),
