@@ -10,7 +10,7 @@ master weights, 8-bit states).  Timed on the device with CUDA events, max over
 ranks; every iteration touches far more than the 126 MB L2.
 
 The ``*_push`` variants also store the updated bf16 shard into every rank's parameter buffer
-(all-gather on write); compare them with ``nccl_then_step`` plus an all-gather of the shard.
+(all-gather on write); their baseline is ``nccl_then_step_then_all_gather``.
 
 Roofline of the fused kernel = the slower of
   * NVLink: bytes per direction per GPU / 770 GB/s (measured peer-copy rate).  With peer
