@@ -46,3 +46,32 @@ def test_ctypes_structures_match_the_header(tmp_path):
     # every member of the header is mirrored (a member missing in Python would shift nothing
     # before it but shrink the structure)
     assert ctypes.sizeof(native.FoSeg) == 64
+
+
+def _declared_functions():
+    import re
+
+    decls = {}
+    for header in ("fo_api.h", "fo_noalloc.h"):
+        text = open(os.path.join(ROOT, "flashoptim_b200", "csrc", header)).read()
+        text = re.sub(r"//[^\n]*", "", text)
+        for m in re.finditer(r"\b(?:int|void)\s+(fo_\w+)\s*\(([^)]*)\)\s*;", text):
+            args = m.group(2).strip()
+            decls[m.group(1)] = 0 if args in ("", "void") else args.count(",") + 1
+    return decls
+
+
+def test_every_exported_function_is_declared_with_the_right_arity():
+    try:
+        lib = native.load()
+    except Exception as e:  # library not built on this machine
+        pytest.skip(f"native library unavailable: {e}")
+    decls = _declared_functions()
+    assert len(decls) >= 15
+    checked = 0
+    for name, n_args in decls.items():
+        fn = getattr(lib, name)  # AttributeError: declared in the header but not exported
+        if fn.argtypes is not None:
+            assert len(fn.argtypes) == n_args, name
+            checked += 1
+    assert checked >= 12
