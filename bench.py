@@ -65,8 +65,8 @@ def parse_args():
                     help="with the parameter push: GiB of persistent all-gather buffers per GPU (0: every group)")
     ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
                     help="fused path: NVSwitch multimem.ld_reduce (on) or peer loads summed in fp32 (off); "
-                         "auto = peer loads up to 4 GPUs, multimem above (the faster one in the "
-                         "fused-collective microbenchmark at each size)")
+                         "auto = peer loads at 2 GPUs, multimem above (the configurations this "
+                         "benchmark has been measured in)")
     ap.add_argument("--no-multicast", action="store_true", help="same as --multicast off")
     return ap.parse_args()
 
@@ -229,7 +229,7 @@ def main():
                              master_weight_bits=mwb, compress_state_dict=args.compress_state_dict)
     fused_comm = False
     fused_state = None
-    use_multicast = (world > 4) if args.multicast == "auto" else args.multicast == "on"
+    use_multicast = (world > 2) if args.multicast == "auto" else args.multicast == "on"
     if args.no_multicast:
         use_multicast = False
     push_params = (world == 2) if args.push_params == "auto" else args.push_params == "on"
