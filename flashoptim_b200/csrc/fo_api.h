@@ -118,9 +118,10 @@ enum { FO_MAX_PEERS = 8 };
 //   multicast    NVSwitch multicast mapping of the same buffer, or null: when set,
 //                full aligned units are fetched with multimem.ld_reduce
 //   pad[r]       rank r's signal pad: uint32 words [channel * FO_MAX_PEERS + src]
-//   status       3 local uint32 words, zeroed by the host before first use:
+//   status       4 local uint32 words, zeroed by the host before first use:
 //                [0] bit mask of channels whose wait timed out, [1] 1 + rank that
-//                was missing, [2] CTA counter (internal)
+//                was missing, [2] CTA counter of the step / reduce kernels, [3] CTA counter
+//                of the all-gather kernel (internal; the two families may overlap in time)
 //   epoch        value published / awaited on the channels; grows by one per use
 //   ready_channel  flag "my buffer holds this epoch's gradients"
 //   done_channel   flag "I have finished reading everybody's buffer for this epoch"

@@ -85,15 +85,18 @@ __device__ __forceinline__ bool start_barrier(const FoCommArgs& A) {
 
 // After the main loop: the last CTA to finish tells every peer that this rank
 // no longer reads their buffers for `epoch` (done channel).
-__device__ __forceinline__ void end_signal(const FoCommArgs& A) {
+// `counter` selects the status word that counts finished CTAs: kernels that may run at the
+// same time on one GPU (a step kernel on the reduce-scatter stream and an all-gather on the
+// all-gather stream) must not share one.
+__device__ __forceinline__ void end_signal(const FoCommArgs& A, int counter = 2) {
   __shared__ int last;
   __syncthreads();
   if (threadIdx.x == 0) {
     if (A.push) __threadfence_system();  // this CTA's stores into the peers' memory
     else __threadfence();
-    unsigned int n = atomicAdd(reinterpret_cast<unsigned int*>(A.status) + 2, 1u);
+    unsigned int n = atomicAdd(reinterpret_cast<unsigned int*>(A.status) + counter, 1u);
     last = (n == gridDim.x - 1);
-    if (last) reinterpret_cast<unsigned int*>(A.status)[2] = 0;  // ready for the next launch
+    if (last) reinterpret_cast<unsigned int*>(A.status)[counter] = 0;  // ready for the next launch
   }
   __syncthreads();
   if (last && threadIdx.x < A.world) {
@@ -432,7 +435,7 @@ __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
          i += (int64_t)gridDim.x * kCommThreads)
       dst[i] = src[i];
   }
-  end_signal(A);
+  end_signal(A, 3);
 }
 
 // Stand-alone flag operations (one CTA).
