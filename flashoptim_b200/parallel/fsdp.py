@@ -333,6 +333,22 @@ class FusedFSDPState:
             m.set_custom_reduce_scatter(comm)
         for m, gather in installs:
             m.set_custom_all_gather(gather)
+        self._installs = installs
+        self._listener = on_local_update if push_params else None
+
+    def remove(self) -> None:
+        """Hand the model back to FSDP2's own collectives (collective: call on every rank,
+        between steps).  The symmetric buffers live until this object is dropped."""
+        from torch.distributed.fsdp._fully_shard._fsdp_collectives import DefaultAllGather, DefaultReduceScatter
+
+        for m, _ in self.comms:
+            m.set_custom_reduce_scatter(DefaultReduceScatter())
+        for m, _ in self._installs:
+            m.set_custom_all_gather(DefaultAllGather())
+        self._installs = []
+        if self._listener is not None and self._listener in self.optimizer._local_update_listeners:
+            self.optimizer._local_update_listeners.remove(self._listener)
+        self._listener = None
 
     def check(self) -> None:
         self.peers.check_status()
@@ -374,5 +390,20 @@ def enable_fused_fsdp(
     """
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return None
-    return FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas, own_all_gather,
-                          push_params, push_budget_bytes)
+    state, error = None, None
+    try:
+        state = FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas, own_all_gather,
+                               push_params, push_budget_bytes)
+    except (ValueError, TypeError):
+        raise  # wrong use, raised before any collective and identically on every rank
+    except Exception as e:  # e.g. an allocation that failed on this rank only
+        error = e
+    # all ranks or none: a rank that stayed on NCCL would never answer the others' kernels
+    device = next(model.parameters()).device
+    ok = torch.tensor([0 if state is None else 1], dtype=torch.int32, device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    if int(ok.item()) == 0:
+        if state is not None:
+            state.remove()
+        raise RuntimeError("the fused FSDP2 path could not be set up on every rank") from error
+    return state

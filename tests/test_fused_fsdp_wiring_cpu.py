@@ -165,6 +165,22 @@ def _worker(rank, world):
                     errors.append(f"{tag}: the all-gather after a local step moved no data")
         elif state.ag_eliminated or state.gathers:
             errors.append(f"{tag}: all-gathers were touched without push_params")
+        # remove(): the next step runs on FSDP2's own collectives and still matches
+        if not release:
+            calls = (state.fused_calls, state.ag_eliminated)
+            state.remove()
+            x, y = data[0]
+            xs, ys = x[rank * 4:(rank + 1) * 4].bfloat16(), y[rank * 4:(rank + 1) * 4]
+            for model, opt in ((plain, o1), (fused, o2)):
+                nn.functional.cross_entropy(model(xs).float(), ys).backward()
+                opt.step()
+                opt.zero_grad()
+            if (state.fused_calls, state.ag_eliminated) != calls:
+                errors.append(f"{tag}: the fused path still ran after remove()")
+            if not push:  # (with push the fused model took one extra local step above)
+                for (n1, p1), (_, p2) in zip(plain.named_parameters(), fused.named_parameters()):
+                    errors += check_similar(p2.detach().full_tensor(), p1.detach().full_tensor(), tol,
+                                            f"{tag} after remove {n1}")
     # a user's all-reduce hook post-processes the reduce-scatter output: leave those groups alone
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
