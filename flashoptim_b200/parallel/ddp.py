@@ -25,12 +25,14 @@ hook on unsynchronised backwards and the bucket later holds the accumulated sum.
 
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
 import torch.distributed as dist
 from torch.nn.parallel import DistributedDataParallel as DDP
 
+from ..ops import native
 from ..optim.base import FlashOptimizer
 from .symm import PeerGradients, PeerGroup
 
@@ -102,10 +104,6 @@ class FusedDDPState:
             # rank's second half; after all "done" flags the whole averaged bucket is local
             # and one local multi-tensor step consumes it.  Per GPU this moves 2(W-1)/W of the
             # bucket over NVLink instead of W-1 times the bucket.
-            import ctypes
-
-            from ..ops import native
-
             with torch.cuda.stream(self.side):
                 args = self.grads.next_args()
                 rc = native.load().fo_reduce_bcast_peer(
@@ -165,7 +163,18 @@ def fuse_ddp_allreduce(
     """
     if not isinstance(ddp_model, DDP):
         raise TypeError("fuse_ddp_allreduce expects a DistributedDataParallel model")
-    state = FusedDDPState(ddp_model, optimizer, group, timeout_s, use_multicast, write_back, max_ctas,
-                          two_shot_min_bytes, two_shot)
+    state, error = None, None
+    try:
+        state = FusedDDPState(ddp_model, optimizer, group, timeout_s, use_multicast, write_back, max_ctas,
+                              two_shot_min_bytes, two_shot)
+    except (ValueError, TypeError):
+        raise  # wrong use: the same on every rank, raised before any collective
+    except Exception as e:  # e.g. an allocation that failed on this rank only
+        error = e
+    # all ranks or none (and before the hook is registered: DDP cannot unregister one)
+    ok = torch.tensor([0 if state is None else 1], dtype=torch.int32, device=next(ddp_model.parameters()).device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    if int(ok.item()) == 0:
+        raise RuntimeError("the fused DDP path could not be set up on every rank") from error
     ddp_model.register_comm_hook(state, state.hook)
     return state
