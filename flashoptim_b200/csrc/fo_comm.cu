@@ -88,11 +88,13 @@ __device__ __forceinline__ bool start_barrier(const FoCommArgs& A) {
 // `counter` selects the status word that counts finished CTAs: kernels that may run at the
 // same time on one GPU (a step kernel on the reduce-scatter stream and an all-gather on the
 // all-gather stream) must not share one.
-__device__ __forceinline__ void end_signal(const FoCommArgs& A, int counter = 2) {
+// `remote_stores`: the kernel wrote into other ranks' memory; every CTA then orders its stores
+// at system scope before it counts itself as finished.
+__device__ __forceinline__ void end_signal(const FoCommArgs& A, int counter = 2, bool remote_stores = false) {
   __shared__ int last;
   __syncthreads();
   if (threadIdx.x == 0) {
-    if (A.push) __threadfence_system();  // this CTA's stores into the peers' memory
+    if (remote_stores || A.push) __threadfence_system();  // this CTA's stores into the peers' memory
     else __threadfence();
     unsigned int n = atomicAdd(reinterpret_cast<unsigned int*>(A.status) + counter, 1u);
     last = (n == gridDim.x - 1);
@@ -418,7 +420,7 @@ __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
       }
     }
   }
-  end_signal(A);
+  end_signal(A, 2, true);
 }
 
 // All-gather by pulling: rank r copies slot s of rank s's buffer (at s * slot_bytes)
