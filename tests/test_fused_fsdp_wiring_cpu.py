@@ -109,21 +109,22 @@ def _worker(rank, world):
     fsdp_mod.PeerGroup = _FakePeers
     real_local_listeners = []
 
-    def shard(m):
+    def shard(m, reshard=True):
         for layer in m:
             if isinstance(layer, nn.Linear):
-                fully_shard(layer)
-        fully_shard(m)
+                fully_shard(layer, reshard_after_forward=reshard)
+        fully_shard(m, reshard_after_forward=reshard)
         return m
 
     g = torch.Generator().manual_seed(3)
     data = [(torch.randn(world * 4, 16, generator=g), torch.randint(0, 8, (world * 4,), generator=g))
             for _ in range(4)]
-    for push, release in ((False, False), (True, False), (True, True)):
-        tag = f"push={push} release={release}"
+    for push, release, reshard in ((False, False, True), (True, False, True), (True, True, True),
+                                   (True, False, False)):
+        tag = f"push={push} release={release} reshard={reshard}"
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")
-            plain, fused = shard(_net()), shard(_net())
+            plain, fused = shard(_net(), reshard), shard(_net(), reshard)
             o1 = FlashAdamW(plain.parameters(), lr=5e-4)
             o2 = FlashAdamW(fused.parameters(), lr=5e-4)
         o2.step_from_peers = lambda params, slot, _o=o2: _fake_step_from_peers(_o, params, slot)
