@@ -239,7 +239,7 @@ def main():
         try:
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
-            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=60.0, max_ctas=args.comm_ctas,
+            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=20.0, max_ctas=args.comm_ctas,
                                                     use_multicast=use_multicast, own_all_gather=args.own_all_gather,
                                                     push_params=push_params,
                                                     push_budget_bytes=int(args.push_budget_gb * 2**30) or None)
@@ -271,9 +271,27 @@ def main():
         return fo_step.launch_count()
 
     i = 0
-    for _ in range(args.warmup):
+    fused_error = None
+    for w in range(args.warmup):
         train_step(dev_tokens[i])
         i += 1
+        if w == 0 and fused_state is not None:
+            # After the first step every rank reports whether one of its device-side waits ran
+            # out.  If any did, all ranks hand the model back to NCCL collectives together and
+            # the measurement goes on without the fused path (the JSON line says so).
+            try:
+                fused_state.check()
+            except Exception as e:
+                fused_error = f"{type(e).__name__}: {e}"
+            bad = torch.tensor([0 if fused_error is None else 1], device=dev, dtype=torch.int32)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+            if int(bad.item()):
+                fused_error = fused_error or "a device-side wait ran out on another rank"
+                fused_state.remove()
+                fused_state, fused_comm, push_params = None, False, False
+                if rank == 0:
+                    print(f"[bench] fused FSDP path switched off after the first step: {fused_error}",
+                          file=sys.stderr)
     torch.cuda.synchronize()
     if fused_state is not None:
         fused_state.check()  # raises if a device-side wait for another rank ran out
@@ -367,6 +385,7 @@ def main():
                 "gradient_release": bool(args.gradient_release), "fused_comm": bool(fused_comm),
                 "fused_comm_multicast": bool(fused_comm and use_multicast),
                 "fused_param_push": bool(fused_comm and push_params),
+                **({"fused_comm_error": fused_error} if fused_error else {}),
                 "activation_checkpointing": bool(cfg.activation_checkpointing),
                 "l2": "working set (>= 16 GB of weights) far exceeds the 126 MB L2; no flush",
             },
