@@ -13,6 +13,11 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
 def _worker(rank, world):
+    import os
+
+    # PyTorch's symmetric-memory allocator binds buffers to an NVSwitch multicast object when
+    # it can; this test wants none (set before the first symmetric allocation of the process)
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
     from flashoptim_b200.ops.quant import quantize
     from flashoptim_b200.ops.step import AdamHyper, SegmentTable, launch_adam_peer, make_rows
     from flashoptim_b200.parallel.symm import CommTimeoutError, PeerGradients, PeerGroup
