@@ -42,8 +42,31 @@ def _entry(rank, world, backend, store_path, fn, args, result_dir):
         f.write(err)
 
 
-def run_distributed(fn, world_size=2, backend="gloo", args=()):
-    """Run ``fn(rank, world, *args) -> list[str]`` on ``world_size`` processes; raise on any error."""
+def run_distributed(fn, world_size=2, backend="gloo", args=(), retries=None):
+    """Run ``fn(rank, world, *args) -> list[str]`` on ``world_size`` processes; raise on any error.
+
+    Multi-GPU (``nccl``) runs get one more attempt after a failure: a first failure followed
+    by a pass is reported as a warning carrying the first attempt's messages (one run in seven
+    of a two-GPU kernel test once failed on a fresh machine and never again), a second failure
+    raises.  CPU runs are never repeated."""
+    retries = (1 if backend == "nccl" else 0) if retries is None else retries
+    first = None
+    for attempt in range(retries + 1):
+        try:
+            _run_once(fn, world_size, backend, args)
+        except AssertionError as e:
+            if attempt == retries:
+                raise
+            first = e
+            continue
+        if first is not None:
+            import warnings
+
+            warnings.warn(f"{getattr(fn, '__name__', fn)} failed once and passed when repeated:\n{first}")
+        return
+
+
+def _run_once(fn, world_size, backend, args):
     with tempfile.TemporaryDirectory() as d:
         store = os.path.join(d, "store")
         mp.spawn(_entry, args=(world_size, backend, store, fn, args, d), nprocs=world_size, join=True)
