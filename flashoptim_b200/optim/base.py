@@ -428,6 +428,17 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
             fn()
         return loss
 
+    def _refuse_second_fused_update(self, p: torch.Tensor) -> None:
+        """A collective-fused update is the optimizer step of that backward pass.  A second
+        synchronised backward before ``step()`` / ``step_param()`` has acknowledged the first
+        would update twice where the plain path accumulates and steps once."""
+        if id(p) in self._peer_stepped:
+            raise RuntimeError(
+                "a parameter was updated inside the gradient collective twice without optimizer.step() in "
+                "between; accumulate gradients without synchronisation (DDP no_sync(), FSDP2 "
+                "set_requires_gradient_sync(False)) and synchronise only the last backward pass"
+            )
+
     @torch.no_grad()
     def step_from_peers(self, params: list[torch.Tensor], peer: Any) -> None:
         """Update ``params`` from gradients that still sit, unreduced, in every rank's
@@ -448,6 +459,7 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
                 p_local = local_tensor(p)
                 if p_local.numel() < 1 or not p.requires_grad:
                     continue
+                self._refuse_second_fused_update(p)
                 if not (p_local.is_cuda and p_local.is_contiguous()):
                     raise RuntimeError("steps fused with the collective need contiguous CUDA parameters")
                 if self._check_numerics:
@@ -475,6 +487,7 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
                 p_local = local_tensor(p)
                 if p_local.numel() < 1 or not p.requires_grad:
                     continue
+                self._refuse_second_fused_update(p)
                 if not (p_local.is_cuda and p_local.is_contiguous() and g.is_contiguous()
                         and g.dtype == p_local.dtype and g.numel() == p_local.numel()):
                     raise RuntimeError("step_with_grads needs contiguous CUDA tensors of the parameter's dtype")

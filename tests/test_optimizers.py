@@ -530,3 +530,17 @@ def test_optimizer_state_bytes_per_parameter(cls, kw, mwb, quantize, want):
     p.grad = torch.randn(n).to(torch.bfloat16) * 1e-2
     opt.step()
     assert _state_bytes(opt) / n == pytest.approx(want)
+
+
+def test_second_collective_fused_update_without_step_is_refused():
+    p = nn.Parameter(torch.randn(64).to(torch.bfloat16))
+    opt = FlashAdamW([p], lr=1e-3)
+    opt._peer_stepped.add(id(p))  # what a fused reduce-scatter / all-reduce update leaves behind
+    peer = type("Peer", (), {"offsets": {id(p.data): 0}})()
+    with pytest.raises(RuntimeError, match="twice without optimizer.step"):
+        opt.step_from_peers([p], peer)
+    with pytest.raises(RuntimeError, match="twice without optimizer.step"):
+        opt.step_with_grads([p], [torch.zeros_like(p)])
+    p.grad = torch.zeros_like(p)
+    opt.step()  # acknowledges the fused update (and skips the parameter once)
+    assert id(p) not in opt._peer_stepped
