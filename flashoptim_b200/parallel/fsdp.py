@@ -373,6 +373,9 @@ def enable_fused_fsdp(
     optimizer.  Returns the state object (``.fused_calls`` / ``.fallbacks`` count what
     happened; ``.check()`` raises if a device-side wait timed out), or ``None`` when the
     data-parallel group has a single rank (FSDP2 then performs no reduce-scatter).
+    Every reduce-scatter then IS the optimizer update of that backward pass: accumulate
+    gradients with ``model.set_requires_gradient_sync(False)`` on all but the last
+    micro-batch (a second synchronised backward before ``step()`` raises).
     ``depth`` symmetric buffers of the largest group's gradient size are kept.
     ``max_ctas`` caps the kernel's grid: the reduce-scatter is NVLink-bound, so a few
     dozen CTAs keep the links busy while the SMs stay with backward's GEMMs.
