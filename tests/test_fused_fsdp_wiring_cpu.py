@@ -182,6 +182,29 @@ def _worker(rank, world):
                 for (n1, p1), (_, p2) in zip(plain.named_parameters(), fused.named_parameters()):
                     errors += check_similar(p2.detach().full_tensor(), p1.detach().full_tensor(), tol,
                                             f"{tag} after remove {n1}")
+    # gradient accumulation: only the last micro-batch synchronises, and that reduce-scatter is the update
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        plain, fused = shard(_net()), shard(_net())
+        o1 = FlashAdamW(plain.parameters(), lr=5e-4)
+        o2 = FlashAdamW(fused.parameters(), lr=5e-4)
+    o2.step_from_peers = lambda params, slot, _o=o2: _fake_step_from_peers(_o, params, slot)
+    state = fsdp_mod.enable_fused_fsdp(fused, o2, push_params=True)
+    for step in range(2):
+        for micro, (x, y) in enumerate(data[:2]):
+            xs, ys = x[rank * 4:(rank + 1) * 4].bfloat16(), y[rank * 4:(rank + 1) * 4]
+            for model in (plain, fused):
+                model.set_requires_gradient_sync(micro == 1)
+                nn.functional.cross_entropy(model(xs).float(), ys).backward()
+        for opt in (o1, o2):
+            opt.step()
+            opt.zero_grad()
+        for (n1, p1), (_, p2) in zip(plain.named_parameters(), fused.named_parameters()):
+            errors += check_similar(p2.detach().full_tensor(), p1.detach().full_tensor(),
+                                    get_tolerances(torch.bfloat16, True), f"accumulation step {step} {n1}")
+    if state.fused_calls != 8 or state.fallbacks:
+        errors.append(f"accumulation: {state.fused_calls} fused reduce-scatters, {state.fallbacks} fall-backs")
+
     # a user's all-reduce hook post-processes the reduce-scatter output: leave those groups alone
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
