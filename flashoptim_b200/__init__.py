@@ -7,32 +7,12 @@ public names mirror ``flashoptim/__init__.py:3-33`` of the reference.
 """
 
 from .ops.quant import compute_ecc_bits, dequantize, quantize, reconstruct_fp32_param
-from .optim import (
-    FlashAdam,
-    FlashAdamW,
-    FlashLion,
-    FlashOptimizer,
-    FlashSGD,
-    FlashSGDW,
-    NumericsError,
-)
+from .optim import FlashAdam, FlashAdamW, FlashLion, FlashOptimizer, FlashSGD, FlashSGDW, NumericsError
 from .utils import GradientReleaseHandle, cast_model, enable_gradient_release
 
 __version__ = "0.1.0"
 
-__all__ = [
-    "FlashAdam",
-    "FlashAdamW",
-    "FlashLion",
-    "FlashOptimizer",
-    "FlashSGD",
-    "FlashSGDW",
-    "GradientReleaseHandle",
-    "NumericsError",
-    "compute_ecc_bits",
-    "cast_model",
-    "enable_gradient_release",
-    "reconstruct_fp32_param",
-    "quantize",
-    "dequantize",
-]
+_OPTIMIZERS = ("FlashOptimizer", "FlashSGD", "FlashSGDW", "FlashAdam", "FlashAdamW", "FlashLion", "NumericsError")
+_MODEL_UTILITIES = ("cast_model", "enable_gradient_release", "GradientReleaseHandle")
+_TENSOR_FUNCTIONS = ("quantize", "dequantize", "compute_ecc_bits", "reconstruct_fp32_param")
+__all__ = [*_OPTIMIZERS, *_MODEL_UTILITIES, *_TENSOR_FUNCTIONS]
