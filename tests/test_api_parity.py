@@ -88,3 +88,26 @@ def test_package_exports_every_name_of_the_reference():
             names = ast.literal_eval(node.value)
     assert names and set(names) <= set(fo.__all__)
     assert all(hasattr(fo, n) for n in names)
+
+
+def test_optimizer_base_class_has_every_public_method_of_the_reference():
+    tree = ast.parse(open(os.path.join(REF, "optimizers.py")).read())
+    for node in tree.body:
+        if isinstance(node, ast.ClassDef) and node.name == "FlashOptimizer":
+            methods = [i for i in node.body if isinstance(i, ast.FunctionDef) and not i.name.startswith("_")]
+            break
+    assert len(methods) >= 6
+    for m in methods:
+        ours = getattr(fo.FlashOptimizer, m.name, None)
+        assert callable(ours), m.name
+        want = [a.arg for a in m.args.args if a.arg != "self"]
+        have = [n for n in inspect.signature(ours).parameters if n != "self"]
+        assert have[:len(want)] == want, (m.name, have, want)
+
+
+def test_gradient_release_handle_has_the_reference_members():
+    tree = ast.parse(open(os.path.join(REF, "optimizers.py")).read())
+    for node in tree.body:
+        if isinstance(node, ast.ClassDef) and node.name == "GradientReleaseHandle":
+            members = {i.name for i in node.body if isinstance(i, ast.FunctionDef) and not i.name.startswith("_")}
+    assert members and all(hasattr(fo.GradientReleaseHandle, m) for m in members), members
