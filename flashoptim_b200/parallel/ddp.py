@@ -135,6 +135,10 @@ class FusedDDPState:
         """Synchronise and raise if a device-side wait for another rank timed out."""
         self.peers.check_status()
 
+    def poll(self) -> None:
+        """Non-blocking form of :meth:`check` (reports a timeout one or two calls late)."""
+        self.peers.poll_status()
+
 
 def fuse_ddp_allreduce(
     ddp_model: DDP,

@@ -351,7 +351,12 @@ class FusedFSDPState:
         self._listener = None
 
     def check(self) -> None:
+        """Synchronise and raise if a device-side wait for another rank timed out."""
         self.peers.check_status()
+
+    def poll(self) -> None:
+        """Non-blocking form of :meth:`check` (reports a timeout one or two calls late)."""
+        self.peers.poll_status()
 
 
 def enable_fused_fsdp(

@@ -169,6 +169,33 @@ class PeerGroup:
         native.check(native.load().fo_comm_signal(ctypes.byref(args), channel, native.stream_ptr(self.device)),
                      "fo_comm_signal")
 
+    def poll_status(self) -> None:
+        """Like :meth:`check_status` but never waits for the device: each call inspects the copy
+        of the status words that the previous call requested (if that copy has arrived) and
+        requests a fresh one on the current stream.  A wait that ran out is therefore reported
+        one or two calls late; meant to be called once per training step."""
+        pending = getattr(self, "_poll", None)
+        if pending is not None:
+            host, event = pending
+            if event is None or event.query():
+                self._poll = None
+                st = host.tolist()
+                if st[0] != 0:
+                    self.status.zero_()
+                    raise CommTimeoutError(
+                        f"rank {self.rank}: wait on channel mask {st[0]:#x} timed out (missing rank {st[1] - 1})"
+                    )
+        if getattr(self, "_poll", None) is None:
+            if self.status.is_cuda:
+                if getattr(self, "_poll_host", None) is None:
+                    self._poll_host = torch.empty(4, dtype=torch.int32).pin_memory()
+                self._poll_host.copy_(self.status, non_blocking=True)
+                event = torch.cuda.Event()
+                event.record()
+                self._poll = (self._poll_host, event)
+            else:
+                self._poll = (self.status.clone(), None)
+
     def check_status(self) -> None:
         """Synchronise and raise :class:`CommTimeoutError` if any device-side wait ran out."""
         torch.cuda.synchronize(self.device)

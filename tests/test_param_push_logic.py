@@ -91,3 +91,20 @@ def test_push_budget_takes_groups_in_order_while_they_fit():
     assert select_push_groups([10, 0, 20, 30], None) == [True, False, True, True]
     assert select_push_groups([10, 20, 30, 5], 35) == [True, True, False, True]
     assert select_push_groups([10, 20], 0) == [False, False]
+
+
+def test_poll_status_reports_a_timeout_one_call_late_without_waiting():
+    import pytest
+
+    from flashoptim_b200.parallel.symm import CommTimeoutError, PeerGroup
+
+    peers = PeerGroup(device=torch.device("cpu"))   # one rank, host tensors: no symmetric memory needed
+    peers.poll_status()
+    peers.poll_status()                              # nothing recorded: stays quiet
+    peers.status[0], peers.status[1] = 1 << 3, 2     # what a kernel writes when rank 1 never shows up
+    peers.poll_status()                              # still the older copy
+    with pytest.raises(CommTimeoutError, match="missing rank 1"):
+        peers.poll_status()
+    assert int(peers.status[0]) == 0                 # cleared for the next use
+    peers.poll_status()
+    peers.poll_status()
