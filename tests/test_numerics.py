@@ -156,3 +156,65 @@ def test_min_expressible_step():
     assert oracle.log2_min_expressible_step(torch.bfloat16, 1.0, 3) == pytest.approx(v - 8)
     assert oracle.log2_min_expressible_step(torch.bfloat16, 1.0, 4) == pytest.approx(v - 16)
     assert oracle.log2_min_expressible_step(torch.bfloat16, 4.5, 0) == pytest.approx(v + 2)
+
+
+# ---------------------------------------------------------------- property-based (hypothesis)
+
+hypothesis = pytest.importorskip("hypothesis")
+from hypothesis import given, settings  # noqa: E402
+from hypothesis import strategies as st  # noqa: E402
+
+_finite = st.floats(min_value=-6.0e4, max_value=6.0e4, allow_nan=False, allow_infinity=False, width=32)
+
+
+@settings(max_examples=300, deadline=None, derandomize=True)
+@given(st.lists(_finite, min_size=1, max_size=200), st.sampled_from(MODES))
+def test_quantiser_error_is_bounded_for_any_input(values, mode):
+    """Whatever the values (mixed magnitudes, zeros, a single huge outlier per group, ragged
+    tail): every element comes back within half a code step of its group's absmax (times the
+    compander's slope), plus the fp16 rounding of the scale."""
+    signed, sqrt, softsign = mode
+    x = torch.tensor(values, dtype=torch.float32)
+    if not signed:
+        x = x.abs()
+    q, s = quantize(x, signed=signed, sqrt=sqrt, softsign=softsign)
+    assert q.shape == x.shape and s.numel() == (x.numel() + 31) // 32
+    assert q.dtype == (torch.int8 if signed else torch.uint8)
+    y = dequantize(q, s, signed=signed, sqrt=sqrt, softsign=softsign)
+    assert torch.isfinite(y).all()
+    pad = (-x.numel()) % 32
+    xa = torch.nn.functional.pad(x.abs(), (0, pad)).view(-1, 32)
+    absmax = xa.max(dim=1).values.repeat_interleave(32)[: x.numel()]
+    levels = 127.0 if signed else 255.0
+    # scales are stored in fp16: below 6.1e-5 they are subnormal (spacing 6e-8, zero below 3e-8),
+    # which bounds the error absolutely instead of relatively for tiny groups
+    tiny = 3.0e-8
+    if sqrt:
+        # codes live in the sqrt domain: sqrt(y) is within half a step of sqrt(x)
+        step = absmax.sqrt() * ((2.0 if softsign else 1.0) * 0.5 / levels) * (1 + 1e-3) + 1e-30
+        assert ((y.sqrt() - x.sqrt()).abs() <= step + absmax.sqrt() * 2.0 ** -10 + tiny).all()
+    else:
+        slope = 2.0 if softsign else 1.0   # d(inverse compander)/dy is at most 2 (at |y| = 1)
+        step = absmax * (slope * 0.5 / levels)
+        assert ((y - x).abs() <= step * (1 + 1e-3) + absmax * 2.0 ** -10 + tiny).all()
+    if signed:
+        assert (torch.sign(y) * torch.sign(x) >= 0).all()   # a value never changes sign
+
+
+@settings(max_examples=300, deadline=None, derandomize=True)
+@given(st.lists(st.floats(min_value=-(2.0 ** 127), max_value=2.0 ** 127, allow_nan=False, width=32), min_size=1,
+                max_size=64),
+       st.sampled_from([torch.bfloat16, torch.float16]), st.sampled_from([3, 4]))
+def test_master_weight_split_never_hurts_for_any_input(values, dtype, mbw):
+    x = torch.tensor(values, dtype=torch.float32)
+    w = x.to(dtype)
+    keep = torch.isfinite(w.float())
+    x, w = x[keep], w[keep]
+    if x.numel() == 0:
+        return
+    e = compute_ecc_bits(x, w, master_bytewidth=mbw)
+    r = reconstruct_fp32_param(w, e)
+    assert torch.isfinite(r).all()
+    ulp32 = torch.exp2(torch.floor(torch.log2(x.abs().clamp_min(2.0 ** -126))) - 23)
+    assert ((r - x).abs() <= (w.float() - x).abs() + ulp32).all()
+    assert e.to(torch.int32).abs().max() <= (127 if mbw == 3 else 32767)
