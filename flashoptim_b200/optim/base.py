@@ -307,6 +307,10 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         if self._check_numerics and self._transient_state.get(id(p), {}).get("maxabs") is None:
             self._recompute_stats_for_param(p)
         state = self.state[p]
+        ready = self.__dict__.setdefault("_state_ready", set())
+        if state and id(p) in ready:
+            return  # created (or loaded) earlier; an emptied state is rebuilt below
+        ready.add(id(p))
         p_local = local_tensor(p)
         quantize = hparams.get("quantize", self._quantize)
         for key, spec in self._quantized_state_spec().items():
@@ -636,6 +640,7 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         self.__dict__.setdefault("_local_update_listeners", [])
         self._tables.clear()
         self._transient_state.clear()
+        self.__dict__.setdefault("_state_ready", set()).clear()
         opt_state = cast(dict[torch.Tensor, Any], state["state"])
         for group in cast(list[dict[str, Any]], state["param_groups"]):
             for param in group["params"]:
