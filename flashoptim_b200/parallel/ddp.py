@@ -159,6 +159,8 @@ def fuse_ddp_allreduce(
     ``optimizer.step()`` / ``zero_grad()`` as usual: parameters updated by the hook
     are skipped there.  ``write_back=True`` also stores the averaged gradient back
     into the bucket (needed only if something else reads ``p.grad``).
+    Like gradient release, the hook updates parameters during backward, so it excludes
+    ``torch.amp.GradScaler`` and global gradient clipping.
     ``use_multicast`` fetches through NVSwitch ``multimem.ld_reduce``; the default
     uses peer loads in rank order, which guarantees bit-identical replicas.
     With more than two ranks, buckets of at least ``two_shot_min_bytes`` take the two-shot

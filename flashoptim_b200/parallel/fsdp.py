@@ -378,6 +378,9 @@ def enable_fused_fsdp(
     optimizer.  Returns the state object (``.fused_calls`` / ``.fallbacks`` count what
     happened; ``.check()`` raises if a device-side wait timed out), or ``None`` when the
     data-parallel group has a single rank (FSDP2 then performs no reduce-scatter).
+    Like gradient release, this updates parameters during backward, so it excludes loss
+    scaling with ``torch.amp.GradScaler`` and global gradient clipping (both need all
+    gradients before any update).
     Every reduce-scatter then IS the optimizer update of that backward pass: accumulate
     gradients with ``model.set_requires_gradient_sync(False)`` on all but the last
     micro-batch (a second synchronised backward before ``step()`` raises).
