@@ -26,9 +26,7 @@ import argparse
 import importlib.util
 import json
 import os
-import statistics
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -54,7 +52,32 @@ def parse_args():
     ap.add_argument("--activation-checkpointing", action="store_true")
     ap.add_argument("--fused-comm", default="auto", choices=["auto", "off"],
                     help="ours only: fuse the FSDP2 collectives with the update where supported")
-    ap.add_argument("--comm-ctas", type=int, default=0, help="grid cap of the fused reduce-scatter kernel")
+    ap.add_argument("--comm-ctas", type=int, default=-1,
+                    help="grid cap of the fused reduce-scatter kernel (0: fill the GPU; -1: the measured default, "
+                         "see DEFAULT_COMM_CTAS)")
+    ap.add_argument("--sweep", default=None,
+                    help="ours, >= 2 GPUs: instead of the benchmark line, time every listed configuration in this "
+                         "one process and print them as one JSON line.  Semicolon-separated entries "
+                         "MODE[:CTAS[:LOADS]] with MODE nccl (FSDP2's NCCL collectives + this library's step), "
+                         "fused (reduce-scatter fused with the update) or push (fused + all-gather on write), "
+                         "CTAS the grid cap (0: none) and LOADS mc (multimem.ld_reduce), p2p (peer loads into "
+                         "registers) or staged (bulk copies of the peers' chunks into shared memory); p2pmc / stagedmc "
+                         "push the parameters with multimem.st instead of one store per rank; ce / cestaged move all "
+                         "bytes with the copy engines and run the register / staged kernel on local memory; a fourth field "
+                         "capall also caps the group that backward reduces last")
+    ap.add_argument("--transport", default="auto", choices=["auto", "kernel", "copy_engine"],
+                    help="fused path: the update kernel itself reads the peers' gradients over NVLink (kernel) "
+                         "or copy engines bring them into local memory first (copy_engine); auto: the measured "
+                         "default, see DEFAULT_COMM_TRANSPORT")
+    ap.add_argument("--push-multicast", default="auto", choices=["auto", "on", "off"],
+                    help="parameter push through multimem.st (auto: as the gradient loads; with staged kernels "
+                         "above 2 GPUs)")
+    ap.add_argument("--comm-kernel", default="auto", choices=["auto", "register", "staged"],
+                    help="fused path: register-path or bulk-copy staged reduce-scatter + update kernels "
+                         "(auto: the measured default, see DEFAULT_COMM_KERNEL)")
+    ap.add_argument("--timeline", default=None,
+                    help="write a summary of a torch.profiler trace of two steps (kernel time per stream and "
+                         "per kernel family, rank 0) to this file; never a benchmark number")
     ap.add_argument("--own-all-gather", action="store_true",
                     help="fused path: FSDP2's parameter all-gather through this library's pull kernel")
     ap.add_argument("--push-params", default="auto", choices=["auto", "on", "off"],
@@ -71,71 +94,153 @@ def parse_args():
     return ap.parse_args()
 
 
-class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML (read-only) every 200 ms."""
-
-    def __init__(self, index: int):
-        self.samples: list[int] = []
-        self.reasons: set[str] = set()
-        self.max_mhz = None
-        self._stop = threading.Event()
-        self._thread = None
-        try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            self._nv = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
-        except Exception:
-            self._nv = None
-
-    def _run(self):
-        nv = self._nv
-        names = {
-            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
-            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
-            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
-            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
-        }
-        while not self._stop.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
-                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
-                for k, bit in names.items():
-                    if mask & bit:
-                        self.reasons.add(k)
-            except Exception:
-                pass
-            self._stop.wait(0.2)
-
-    def start(self):
-        if self._nv is not None:
-            self._stop.clear()
-            self._thread = threading.Thread(target=self._run, daemon=True)
-            self._thread.start()
-
-    def stop(self):
-        if self._thread is not None:
-            self._stop.set()
-            self._thread.join()
-            self._thread = None
-
-    def summary(self):
-        return {
-            "sm_mhz": statistics.median(self.samples) if self.samples else None,
-            "sm_max_mhz": self.max_mhz,
-            "reasons": sorted(self.reasons),
-            "samples": len(self.samples),
-        }
-
-
 def load_module_from(path: str, name: str):
     spec = importlib.util.spec_from_file_location(name, path)
     mod = importlib.util.module_from_spec(spec)
     sys.modules[name] = mod
     spec.loader.exec_module(mod)
     return mod
+
+
+# Defaults of the fused FSDP2 path by world size, taken from sweeps on 8 x B200
+# (`--sweep`, tables in DESIGN.md): grid cap of the reduce-scatter + update kernel (0: none).
+DEFAULT_COMM_CTAS = {2: 0, 4: 0, 8: 0}
+# All-gather on write keeps one unsharded copy of the parameters per GPU; "auto" turns it on
+# while that copy stays below this many GiB.
+PUSH_AUTO_MAX_GIB = 24.0
+
+
+def default_comm_ctas(world: int, multicast: bool) -> int:
+    del multicast
+    return DEFAULT_COMM_CTAS.get(world, 0)
+
+
+# Bulk-copy staged reduce-scatter + update kernels by world size (same sweeps).
+DEFAULT_COMM_KERNEL = {2: "register", 4: "register", 8: "register"}
+
+
+# Who moves the gradient bytes: the update kernel (peer loads / multimem / bulk copies) or the
+# copy engines (cudaMemcpyAsync into a local staging buffer, then a local update kernel).
+DEFAULT_COMM_TRANSPORT = {2: "kernel", 4: "kernel", 8: "kernel"}
+
+
+def default_comm_staged(world: int) -> bool:
+    return DEFAULT_COMM_KERNEL.get(world, "register") == "staged"
+
+
+def push_default(world: int, n_params: int) -> bool:
+    return world >= 2 and n_params * 2 / 2**30 <= PUSH_AUTO_MAX_GIB
+
+
+def measured_hbm_gbs() -> float:
+    """Copy bandwidth measured on this pool's B200s (the roofline denominator), or the
+    earlier measurement of 6650 GB/s when the file is absent."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def _kernel_family(name: str) -> str:
+    n = name.lower()
+    if n.startswith("fo::") or "fo::" in n:
+        return "flashoptim_b200"
+    if "nccl" in n:
+        return "nccl"
+    if "flash" in n or "fmha" in n or "attention" in n or "sdpa" in n:
+        return "attention"
+    if "gemm" in n or "cutlass" in n or "nvjet" in n or "xmma" in n or "cublas" in n:
+        return "gemm"
+    if "memcpy" in n or "memset" in n:
+        return "memcpy"
+    return "other"
+
+
+def _union_ms(intervals) -> float:
+    total, end = 0.0, None
+    for a, b in sorted(intervals):
+        if end is None or a > end:
+            total += b - a
+            end = b
+        elif b > end:
+            total += b - end
+            end = b
+    return total / 1e3
+
+
+def timeline_summary(step_fn, rank: int, path: str, fused_state) -> dict:
+    """Two steps under torch.profiler (CUDA activities only) on rank 0, reduced to: wall time
+    per step, busy time per stream, kernel time per family, and how long the stream that runs
+    the GEMMs sat idle.  With a fused path the same is recorded again with FSDP2's NCCL
+    collectives.  Diagnostic only: nothing measured under a profiler is a benchmark number."""
+    import tempfile
+
+    import torch
+    import torch.distributed as dist
+    from torch.profiler import ProfilerActivity, profile
+
+    def capture(label):
+        for _ in range(2):
+            step_fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        out = None
+        if rank == 0:
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for _ in range(2):
+                    step_fn()
+                torch.cuda.synchronize()
+            with tempfile.TemporaryDirectory() as d:
+                f = os.path.join(d, "trace.json")
+                prof.export_chrome_trace(f)
+                with open(f) as fh:
+                    trace = json.load(fh)
+            ks = [e for e in trace.get("traceEvents", [])
+                  if e.get("ph") == "X" and e.get("cat") in ("kernel", "gpu_memcpy", "gpu_memset")]
+            if ks:
+                t0 = min(e["ts"] for e in ks)
+                t1 = max(e["ts"] + e["dur"] for e in ks)
+                streams, fam, fam_n = {}, {}, {}
+                for e in ks:
+                    sid = e.get("args", {}).get("stream", -1)
+                    name = e["name"] if e.get("cat") == "kernel" else e.get("cat")
+                    k = _kernel_family(name)
+                    streams.setdefault(sid, {"iv": [], "fam": {}})
+                    streams[sid]["iv"].append((e["ts"], e["ts"] + e["dur"]))
+                    streams[sid]["fam"][k] = streams[sid]["fam"].get(k, 0.0) + e["dur"] / 1e3
+                    fam[k] = fam.get(k, 0.0) + e["dur"] / 1e3
+                    fam_n[k] = fam_n.get(k, 0) + 1
+                gemm_stream = max(streams, key=lambda sid: streams[sid]["fam"].get("gemm", 0.0))
+                wall = (t1 - t0) / 1e3
+                out = {
+                    "label": label, "steps": 2, "wall_ms_per_step": round(wall / 2, 2),
+                    "kernel_ms_per_step_by_family": {k: round(v / 2, 2) for k, v in sorted(fam.items())},
+                    "launches_per_step_by_family": {k: v / 2 for k, v in sorted(fam_n.items())},
+                    "compute_stream": gemm_stream,
+                    "compute_stream_idle_ms_per_step": round((wall - _union_ms(streams[gemm_stream]["iv"])) / 2, 2),
+                    "streams": {str(sid): {"busy_ms_per_step": round(_union_ms(v["iv"]) / 2, 2),
+                                           "kernel_ms_per_step_by_family": {k: round(x / 2, 2) for k, x in v["fam"].items()}}
+                                for sid, v in streams.items()},
+                }
+        else:
+            for _ in range(2):
+                step_fn()
+            torch.cuda.synchronize()
+        dist.barrier()
+        return out
+
+    records = [capture("default configuration")]
+    if fused_state is not None:
+        saved = (fused_state.enabled, fused_state.push_enabled)
+        fused_state.enabled, fused_state.push_enabled = False, False
+        records.append(capture("FSDP2's NCCL collectives + this library's step"))
+        fused_state.enabled, fused_state.push_enabled = saved
+    if rank == 0:
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        with open(path, "w") as f:
+            json.dump(records, f, indent=1)
+    return {"records": len(records)}
 
 
 def main():
@@ -229,19 +334,32 @@ def main():
                              master_weight_bits=mwb, compress_state_dict=args.compress_state_dict)
     fused_comm = False
     fused_state = None
+    if args.sweep and (args.impl != "ours" or world < 2):
+        raise SystemExit("--sweep compares this library's collective paths: it needs --impl ours and >= 2 GPUs")
     use_multicast = (world > 2) if args.multicast == "auto" else args.multicast == "on"
     if args.no_multicast:
         use_multicast = False
-    push_params = (world == 2) if args.push_params == "auto" else args.push_params == "on"
+    push_params = push_default(world, n_params) if args.push_params == "auto" else args.push_params == "on"
     if args.own_all_gather:
         push_params = False
+    comm_ctas = default_comm_ctas(world, use_multicast) if args.comm_ctas < 0 else args.comm_ctas
+    staged = default_comm_staged(world) if args.comm_kernel == "auto" else args.comm_kernel == "staged"
+    if staged and args.multicast != "on":
+        use_multicast = False  # the staged kernels read the peers' buffers with bulk copies
+    transport = DEFAULT_COMM_TRANSPORT.get(world, "kernel") if args.transport == "auto" else args.transport
+    if transport == "copy_engine" and args.multicast != "on":
+        use_multicast = False
+    push_mc = (use_multicast or (staged and world > 2)) if args.push_multicast == "auto" else args.push_multicast == "on"
+    if args.sweep:  # every variant must be reachable by flipping switches at run time
+        use_multicast, push_params = True, True
     if args.impl == "ours" and args.fused_comm == "auto":
         try:
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
-            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=20.0, max_ctas=args.comm_ctas,
+            fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=20.0, max_ctas=comm_ctas,
                                                     use_multicast=use_multicast, own_all_gather=args.own_all_gather,
-                                                    push_params=push_params,
+                                                    push_params=push_params, staged=staged, push_multicast=push_mc,
+                                                    transport=transport,
                                                     push_budget_bytes=int(args.push_budget_gb * 2**30) or None)
             fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
@@ -296,22 +414,82 @@ def main():
     if fused_state is not None:
         fused_state.check()  # raises if a device-side wait for another rank ran out
     torch.cuda.reset_peak_memory_stats()
-    sampler = ClockSampler(local_rank)
+    # read-only NVML sampler, loaded by path like the model file (no package import in the reference arm)
+    timing = load_module_from(os.path.join(ROOT, "flashoptim_b200", "utils", "timing.py"), "_bench_timing")
+    sampler = timing.ClockSampler(local_rank)
+
+    def timed_steps(n: int) -> float:
+        """ms per step of ``n`` steps on resident inputs: CUDA events, barrier + synchronize on
+        both sides, maximum over ranks."""
+        nonlocal i
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(n):
+            train_step(dev_tokens[i % total_steps])
+            i += 1
+        t1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = torch.tensor([t0.elapsed_time(t1) / n], device=dev, dtype=torch.float64)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    if args.sweep:
+        if fused_state is None:
+            raise SystemExit(f"--sweep: the fused path could not be set up ({fused_error})")
+        sampler.start()
+        results = []
+        for entry in args.sweep.split(";"):
+            f = entry.strip().split(":")
+            mode = f[0]
+            ctas = int(f[1]) if len(f) > 1 and f[1] else 0
+            loads = f[2] if len(f) > 2 and f[2] else "mc"
+            cap_all = len(f) > 3 and f[3] == "capall"
+            if mode not in ("nccl", "fused", "push") or loads not in ("mc", "p2p", "p2pmc", "staged", "stagedmc",
+                                                                      "ce", "cestaged"):
+                raise SystemExit(f"--sweep: bad entry {entry!r}")
+            fused_state.enabled = mode != "nccl"
+            fused_state.push_enabled = mode == "push"
+            fused_state.peers.max_ctas = ctas
+            fused_state.peers.use_multicast = loads == "mc"
+            fused_state.peers.variant = 1 if "staged" in loads else 0
+            fused_state.transport = "copy_engine" if loads.startswith("ce") else "kernel"
+            fused_state.peers.push_multicast = loads.endswith("mc")
+            fused_state.comms[0][1].full_grid = not cap_all and len(fused_state.comms) > 1
+            for _ in range(2):  # settle: the first step after a switch still runs the old all-gathers
+                train_step(dev_tokens[i % total_steps])
+                i += 1
+            fused_state.check()
+            c0 = (fused_state.fused_calls, fused_state.fallbacks, fused_state.ag_eliminated, fused_state.ag_fallbacks)
+            torch.cuda.reset_peak_memory_stats()
+            ms = timed_steps(args.steps)
+            fused_state.check()
+            c1 = (fused_state.fused_calls, fused_state.fallbacks, fused_state.ag_eliminated, fused_state.ag_fallbacks)
+            results.append({
+                "entry": entry.strip(), "mode": mode, "comm_ctas": ctas, "loads": loads if mode != "nccl" else None,
+                "last_group_full_grid": not cap_all,
+                "ms_per_step": round(ms, 3), "tokens_per_s": round(world * b * s / (ms * 1e-3), 1),
+                "peak_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2),
+                "per_step": {k: (y - x) / args.steps for k, x, y in
+                             zip(("fused_rs", "nccl_rs", "ag_eliminated", "nccl_ag"), c0, c1)},
+            })
+            if rank == 0:
+                print(f"[sweep] {results[-1]}", file=sys.stderr, flush=True)
+        sampler.stop()
+        if rank == 0:
+            print(json.dumps({"sweep": results, "n_gpus": world, "steps": args.steps, "model": args.model,
+                              "seq_len": s, "optimizer": args.optimizer, "master_weight_bits": mwb,
+                              "gradient_release": bool(args.gradient_release), "clocks": sampler.summary()}),
+                  flush=True)
+        dist.destroy_process_group()
+        return
 
     # ---- device-timed loop (inputs resident on the device)
-    dist.barrier()
-    torch.cuda.synchronize()
     sampler.start()
     l0 = launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        train_step(dev_tokens[i])
-        i += 1
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    dev_ms = e0.elapsed_time(e1) / args.steps
+    dev_ms = timed_steps(args.steps)
     n_launch = launches() - l0
 
     # ---- end-to-end loop: pinned-host inputs in, loss out, every step
@@ -320,7 +498,7 @@ def main():
     t0 = time.perf_counter()
     last_loss = 0.0
     for _ in range(args.steps):
-        tok = host_tokens[i].to(dev, non_blocking=True)
+        tok = host_tokens[i % total_steps].to(dev, non_blocking=True)
         last_loss = float(train_step(tok).item())
         i += 1
     torch.cuda.synchronize()
@@ -329,6 +507,49 @@ def main():
     if fused_state is not None:
         fused_state.check()
     dist.barrier()
+    peak_bytes = torch.cuda.max_memory_allocated()
+
+    # ---- the optimizer step alone (the second half of the headline metric): gradients of one
+    # more backward pass are kept and optimizer.step() is timed on them, on this rank's shards
+    step_stats = None
+    if not args.gradient_release:
+        if fused_state is not None:
+            fused_state.enabled = False  # this backward leaves its gradients to optimizer.step()
+        model(dev_tokens[i % total_steps][:, :-1], dev_tokens[i % total_steps][:, 1:]).backward()
+        i += 1
+        opt.step()  # untimed: after a switch of paths the segment tables are rebuilt once
+        torch.cuda.synchronize()
+        reps = 10
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+        ev[0].record()
+        for k in range(reps):
+            opt.step()
+            ev[k + 1].record()
+        torch.cuda.synchronize()
+        times = sorted(ev[k].elapsed_time(ev[k + 1]) for k in range(reps))
+        opt.zero_grad(set_to_none=True)
+        if fused_state is not None:
+            fused_state.enabled = True
+        local_elems = sum((p._local_tensor if hasattr(p, "_local_tensor") else p).numel() for p in model.parameters())
+        t = torch.tensor([times[reps // 2]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        step_ms = float(t.item())
+        state_bytes = {"adamw": 4.25, "lion": 2.125}[args.optimizer]  # 8-bit codes + fp16 scale per 32, r+w
+        ecc_bytes = {None: 0, 24: 2, 32: 4}[mwb]
+        bytes_per_elem = 2 + 2 + 2 + state_bytes + ecc_bytes  # param r+w, grad r, states, correction r+w
+        step_stats = {
+            "step_ms": round(step_ms, 3),
+            "step_ms_per_1b": round(step_ms / (local_elems / 1e9), 3),
+            "step_hbm_frac": round(bytes_per_elem * local_elems / (step_ms * 1e-3) / (measured_hbm_gbs() * 1e9), 3),
+            "step_local_params": local_elems,
+            "step_bytes_per_param": bytes_per_elem,
+            "step_timing": f"median of {reps} optimizer.step() calls, CUDA events, max over ranks; HBM fraction of "
+                           f"the measured copy bandwidth {measured_hbm_gbs()} GB/s",
+        }
+
+    timeline = None
+    if args.timeline:
+        timeline = timeline_summary(lambda: train_step(dev_tokens[i % total_steps]), rank, args.timeline, fused_state)
 
     dcp_times = None
     if args.dcp_dir:
@@ -359,9 +580,9 @@ def main():
         dcp_times = {"save_s": round(t1 - t0, 3), "load_s": round(t2 - t1, 3), "bytes_on_disk": size,
                      "compressed": bool(args.compress_state_dict)}
 
-    t = torch.tensor([dev_ms, e2e_ms, torch.cuda.max_memory_allocated() / 2**30], device=dev, dtype=torch.float64)
+    t = torch.tensor([e2e_ms, peak_bytes / 2**30], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms, peak_gib = (float(x) for x in t.tolist())
+    e2e_ms, peak_gib = (float(x) for x in t.tolist())
     tokens_per_step = world * b * s
     if rank == 0:
         rec = {
@@ -385,6 +606,9 @@ def main():
                 "gradient_release": bool(args.gradient_release), "fused_comm": bool(fused_comm),
                 "fused_comm_multicast": bool(fused_comm and use_multicast),
                 "fused_param_push": bool(fused_comm and push_params),
+                "fused_comm_ctas": comm_ctas if fused_comm else None,
+                "fused_comm_kernel": ("staged" if staged else "register") if fused_comm else None,
+                "fused_comm_transport": transport if fused_comm else None,
                 **({"fused_comm_error": fused_error} if fused_error else {}),
                 "activation_checkpointing": bool(cfg.activation_checkpointing),
                 "l2": "working set (>= 16 GB of weights) far exceeds the 126 MB L2; no flush",
@@ -401,8 +625,12 @@ def main():
             "peak_gib_per_gpu": round(peak_gib, 2),
             "clocks": sampler.summary(),
         }
+        if step_stats is not None:
+            rec.update(step_stats)
         if dcp_times is not None:
             rec["dcp"] = dcp_times
+        if timeline is not None:
+            rec["timeline_file"] = args.timeline
         print(json.dumps(rec), flush=True)
     dist.destroy_process_group()
 

@@ -9,6 +9,9 @@ layer).  Rank r reduces row r of every rank and updates its shard (AdamW, 24-bit
 master weights, 8-bit states).  Timed on the device with CUDA events, max over
 ranks; every iteration touches far more than the 126 MB L2.
 
+``fused_peer_loads`` / ``fused_multimem`` are the register-path kernels, ``fused_staged`` the
+bulk-copy staged kernel (``cp.async.bulk`` from the peers' memory into shared memory);
+``--ctas 0,32,64`` times every fused variant at those grid caps (``name@cap``).
 The ``*_push`` variants also store the updated bf16 shard into every rank's parameter buffer
 (all-gather on write); their baseline is ``nccl_then_step_then_all_gather``.
 
@@ -39,6 +42,7 @@ def main():
     ap.add_argument("--numel", type=int, default=218103808)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--ctas", default="0", help="comma-separated grid caps to time every fused variant at (0: none)")
     args = ap.parse_args()
 
     import torch
@@ -49,6 +53,7 @@ def main():
         AdamHyper, SegmentTable, launch_adam, launch_adam_peer, make_rows,
     )
     from flashoptim_b200.parallel.symm import ParamPush, PeerGradients, PeerGroup
+    from flashoptim_b200.utils.timing import ClockSampler
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -87,14 +92,25 @@ def main():
 
     results = {}
     ag_out = torch.empty(n, dtype=torch.bfloat16, device=dev)
-    for name in ("fused_peer_loads", "fused_multimem", "fused_peer_loads_push", "fused_multimem_push",
-                 "nccl_then_step", "nccl_then_step_then_all_gather"):
-        use_mc = "multimem" in name
-        if use_mc and not buf.multicast_ptr:
+    caps = [int(c) for c in args.ctas.split(",")]
+    names = []
+    for base in ("fused_peer_loads", "fused_staged", "fused_multimem", "fused_peer_loads_push", "fused_staged_push",
+                 "fused_staged_push_mc", "fused_multimem_push"):
+        names += [f"{base}@{c}" if c else base for c in caps]
+    names += ["nccl_then_step", "nccl_then_step_then_all_gather"]
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for name in names:
+        kind, _, cap = name.partition("@")
+        use_mc = "multimem" in kind
+        if (use_mc or kind.endswith("_mc")) and not buf.multicast_ptr:
             continue
         pg = PeerGradients(peers, buf, ready, done, grad_scale=1.0 / world)
-        pg.push = push_target if name.endswith("_push") else None
+        pg.push = push_target if "_push" in kind else None
         peers.use_multicast = use_mc
+        peers.push_multicast = use_mc or kind.endswith("_mc")
+        peers.variant = 1 if "staged" in kind else 0
+        peers.max_ctas = int(cap) if cap else 0
         pg.epoch = results.get("_epoch", 0)
         step = [0]
 
@@ -103,7 +119,7 @@ def main():
             if name.startswith("nccl"):
                 dist.reduce_scatter_tensor(rs_out, grads, op=dist.ReduceOp.AVG)
                 launch_adam(table_local, rows_local, torch.bfloat16, 1, True, hyper(step[0], 1.0))
-                if name.endswith("all_gather"):
+                if kind.endswith("all_gather"):
                     dist.all_gather_into_tensor(ag_out, p)
             else:
                 launch_adam_peer(table_peer, rows_peer, torch.bfloat16, 1, True, hyper(step[0], 1.0 / world),
@@ -126,6 +142,7 @@ def main():
         results["_epoch"] = pg.epoch
         dist.barrier()
 
+    sampler.stop()
     if rank == 0:
         peak_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
         hbm = float(json.load(open(peak_path))["hbm_gbs"]) if os.path.exists(peak_path) else 6650.0
@@ -138,14 +155,17 @@ def main():
                 continue
             rec = {"ms": round(ms_, 4)}
             if not name.startswith("nccl"):
-                inbound = shard * 2 * ((world - 1) if "peer_loads" in name else (1 if world > 1 else 0))
+                kind = name.partition("@")[0]
+                pulls = "multimem" not in kind  # peer loads and bulk copies fetch every rank's row
+                stores_mc = "multimem" in kind or kind.endswith("_mc")
+                inbound = shard * 2 * ((world - 1) if pulls else (1 if world > 1 else 0))
                 outbound = shard * 2 * (world - 1)
-                if name.endswith("_push"):
+                if "_push" in kind:
                     # the new shard goes to the other world-1 ranks (peer stores: that many copies
                     # leave this GPU; multimem.st: one copy leaves and the switch replicates it),
                     # and world-1 shards arrive either way
                     inbound += shard * 2 * (world - 1)
-                    outbound += shard * 2 * ((world - 1) if "peer_loads" in name else (1 if world > 1 else 0))
+                    outbound += shard * 2 * ((world - 1) if not stores_mc else (1 if world > 1 else 0))
                 link_ms = max(inbound, outbound) / (link * 1e9) * 1e3
                 roof = max(link_ms, hbm_ms)
                 rec.update({"nvlink_inbound_MB": round(inbound / 1e6, 1),
@@ -153,6 +173,7 @@ def main():
                             "bound": "nvlink" if link_ms > hbm_ms else "hbm",
                             "frac_of_roofline": round(roof / ms_, 3)})
             out[name] = rec
+        out["clocks"] = sampler.summary()
         print(json.dumps(out), flush=True)
     dist.destroy_process_group()
 

@@ -9,11 +9,13 @@ file holding a hash of sources and flags makes repeated calls free.
 
 from __future__ import annotations
 
+import contextlib
 import hashlib
 import os
 import shutil
 import subprocess
 import sys
+import tempfile
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
@@ -64,6 +66,21 @@ def is_current(extra_flags: tuple[str, ...] = ()) -> bool:
     )
 
 
+@contextlib.contextmanager
+def _build_lock(lock_dir: Path):
+    """Exclusive inter-process lock: under torchrun every rank may find the library stale at
+    the same moment, and only one of them may run nvcc into the shared object directory."""
+    lock_dir.mkdir(parents=True, exist_ok=True)
+    with open(lock_dir / ".build.lock", "w") as fh:
+        try:
+            import fcntl
+
+            fcntl.flock(fh, fcntl.LOCK_EX)
+        except ImportError:  # no fcntl: single-process builds only
+            pass
+        yield
+
+
 def build(
     force: bool = False,
     verbose: bool = False,
@@ -85,6 +102,14 @@ def build(
             "nvcc not found: cannot build libflashoptim_b200.so "
             "(set NVCC or CUDA_HOME, or ship a prebuilt _lib/)"
         )
+    with _build_lock(out.parent):
+        # another process may have finished the same build while this one waited
+        if default_target and not force and is_current(extra_flags):
+            return out
+        return _build_locked(nvcc, out, default_target, verbose, extra_flags)
+
+
+def _build_locked(nvcc: str, out: Path, default_target: bool, verbose: bool, extra_flags: tuple[str, ...]) -> Path:
     obj_dir = out.parent / ("obj_" + out.stem)
     obj_dir.mkdir(parents=True, exist_ok=True)
 
@@ -100,16 +125,26 @@ def build(
 
     with ThreadPoolExecutor(max_workers=min(8, len(_sources()) or 1)) as ex:
         objs = list(ex.map(compile_one, _sources()))
-    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(out)] + [
-        str(o) for o in objs
-    ]
-    if verbose:
-        print(" ".join(link), flush=True)
-    r = subprocess.run(link, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    # link beside the target and rename into place: a process that dlopens the library at this
+    # moment sees the old file or the new one, never a half-written one; the stamp comes last
+    fd, tmp = tempfile.mkstemp(prefix=out.stem + ".", suffix=".so.tmp", dir=str(out.parent))
+    os.close(fd)
+    try:
+        link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp] + [str(o) for o in objs]
+        if verbose:
+            print(" ".join(link), flush=True)
+        r = subprocess.run(link, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.chmod(tmp, 0o755)
+        os.replace(tmp, out)
+    finally:
+        if os.path.exists(tmp):
+            os.unlink(tmp)
     if default_target:
-        STAMP_PATH.write_text(source_hash(extra_flags))
+        stamp_tmp = STAMP_PATH.with_suffix(".stamp.tmp")
+        stamp_tmp.write_text(source_hash(extra_flags))
+        os.replace(stamp_tmp, STAMP_PATH)
     return out
 
 

@@ -136,6 +136,11 @@ enum { FO_MAX_PEERS = 8 };
 //                (or once through the multicast mapping param_out_mc), and the kernel then
 //                publishes push_epoch on pushed_channel.  A rank that waits for all ranks'
 //                pushed flags holds every rank's fresh parameters without an all-gather.
+//   variant      step kernels: 1 selects the bulk-copy staged kernels (a producer thread streams
+//                the ranks' gradient chunks and the local state through shared memory with
+//                cp.async.bulk; few CTAs saturate NVLink) for bf16 / fp16 parameters with 8-bit
+//                states and peer loads (multicast null); every other case, and 0, runs the
+//                register-path kernels
 typedef struct FoCommArgs {
   const void* grad[FO_MAX_PEERS];
   const void* multicast;
@@ -154,11 +159,23 @@ typedef struct FoCommArgs {
   int64_t param_out_delta;
   uint32_t push_epoch;
   int pushed_channel;
+  int variant;  // step kernels: 0 register path; 1 bulk-copy staged kernels where they apply
+  int flags;    // FO_COMM_* bits
 } FoCommArgs;
 
-// Elements per CTA iteration of the peer step kernels for a group of `world` ranks (for
-// the chunk prefix): the fewer ranks, the more units a thread keeps in flight.
-int fo_comm_chunk_elems(int world);
+// FoCommArgs.flags, for callers that move the bytes themselves (copy engines) and use the
+// step kernels only for the arithmetic:
+//   NO_BARRIER   the kernel neither publishes "ready" nor waits for it
+//   NO_SIGNAL    the kernel publishes neither "done" nor "pushed"
+//   PUSH_LOCAL   the parameter push stores into param_out[rank] only
+enum { FO_COMM_NO_BARRIER = 1, FO_COMM_NO_SIGNAL = 2, FO_COMM_PUSH_LOCAL = 4 };
+
+// Elements per CTA iteration ("chunk", for the chunk prefix) of the kernel that
+// fo_adam_step_peer / fo_momentum_step_peer will run for these arguments; `q8_states` is
+// `quantized` of the Adam call, or state_mode == FO_STATE_Q8 of the momentum call.  Register
+// path with peer loads: the fewer ranks, the more units a thread keeps in flight; with
+// multimem always four units; staged kernels: one unit.
+int fo_comm_step_chunk_elems(const FoCommArgs* comm, int dtype, int q8_states);
 
 // `segs` and `chunk_begin` are DEVICE pointers.  The gradient of every element
 // is hyper->grad_scale times the sum over ranks (pass 1 / world for a mean).
@@ -183,6 +200,11 @@ int fo_allgather_peer(int64_t slot_bytes, const FoCommArgs* comm, void* stream);
 // Publish / await comm->epoch on one channel from a one-CTA kernel.
 int fo_comm_signal(const FoCommArgs* comm, int channel, void* stream);
 int fo_comm_wait(const FoCommArgs* comm, int channel, void* stream);
+// One-CTA kernel: publish comm->epoch on the ready channel, then await every rank's.
+int fo_comm_barrier(const FoCommArgs* comm, void* stream);
+// cudaMemcpyAsync(device to device) on `stream`: between two mappings of symmetric buffers the
+// driver moves the bytes over NVLink with a copy engine, no SM involved.
+int fo_memcpy_async(void* dst, const void* src, int64_t nbytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -21,299 +21,94 @@
 // out records a code in a local status word, the kernel skips its work and
 // returns normally, and the host raises.  No TMA or multicast-cluster loads
 // are used anywhere in this file.
-#include "fo_step_core.cuh"
+#include "fo_comm.cuh"
 
 namespace fo {
 
-constexpr int kCommThreads = 256;
-constexpr int kCommChunk = kCommThreads * kUnit;
-constexpr int kCommCtasPerSm = 3;
-
-__device__ __forceinline__ uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// Epochs only grow; a flag satisfies a wait once it has reached the epoch
-// (signed difference, so wrap-around after 2^31 steps is harmless).
-__device__ __forceinline__ bool epoch_reached(uint32_t flag, uint32_t epoch) {
-  return (int32_t)(flag - epoch) >= 0;
-}
-
-// Thread `t < world` waits until rank t's flag on `channel` reaches `epoch`.
-// Returns false on timeout (and records it).
-__device__ __forceinline__ bool wait_flag(const FoCommArgs& A, int channel, int src, uint32_t epoch) {
-  const uint32_t* flag = A.pad[A.rank] + channel * FO_MAX_PEERS + src;
-  const uint64_t t0 = global_ns();
-  for (;;) {
-    if (epoch_reached(ld_acquire_sys(flag), epoch)) return true;
-    if (global_ns() - t0 > A.timeout_ns) {
-      atomicOr(reinterpret_cast<unsigned int*>(A.status), 1u << (channel & 31));
-      atomicExch(reinterpret_cast<unsigned int*>(A.status) + 1, (unsigned int)src + 1u);
-      return false;
-    }
-    __nanosleep(64);
-  }
-}
-
-// Every CTA: wait until all ranks have published `epoch` on the ready channel.
-// CTA 0 also publishes this rank's own arrival first.  Returns false (for the
-// whole CTA) if any wait ran out.
-__device__ __forceinline__ bool start_barrier(const FoCommArgs& A) {
-  __shared__ int ok;
-  if (threadIdx.x == 0) ok = 1;
-  __syncthreads();
-  if (blockIdx.x == 0 && threadIdx.x < A.world) {
-    __threadfence_system();
-    st_release_sys(A.pad[threadIdx.x] + A.ready_channel * FO_MAX_PEERS + A.rank, A.epoch);
-  }
-  if (threadIdx.x < A.world) {
-    if (!wait_flag(A, A.ready_channel, threadIdx.x, A.epoch)) ok = 0;
-  }
-  __syncthreads();
-  return ok != 0;
-}
-
-// After the main loop: the last CTA to finish tells every peer that this rank
-// no longer reads their buffers for `epoch` (done channel).
-// `counter` selects the status word that counts finished CTAs: kernels that may run at the
-// same time on one GPU (a step kernel on the reduce-scatter stream and an all-gather on the
-// all-gather stream) must not share one.
-// `remote_stores`: the kernel wrote into other ranks' memory; every CTA then orders its stores
-// at system scope before it counts itself as finished.
-__device__ __forceinline__ void end_signal(const FoCommArgs& A, int counter = 2, bool remote_stores = false) {
-  __shared__ int last;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    if (remote_stores || A.push) __threadfence_system();  // this CTA's stores into the peers' memory
-    else __threadfence();
-    unsigned int n = atomicAdd(reinterpret_cast<unsigned int*>(A.status) + counter, 1u);
-    last = (n == gridDim.x - 1);
-    if (last) reinterpret_cast<unsigned int*>(A.status)[counter] = 0;  // ready for the next launch
-  }
-  __syncthreads();
-  if (last && threadIdx.x < A.world) {
-    __threadfence_system();
-    st_release_sys(A.pad[threadIdx.x] + A.done_channel * FO_MAX_PEERS + A.rank, A.epoch);
-    if (A.push) st_release_sys(A.pad[threadIdx.x] + A.pushed_channel * FO_MAX_PEERS + A.rank, A.push_epoch);
-  }
-}
-
-// ---------------------------------------------------------------- gradient from peers
-
-__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
-  uint4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc_addr)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 multimem_ld_reduce_f16x8(const void* mc_addr) {
-  uint4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc_addr)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 multimem_ld_reduce_f32x4(const void* mc_addr) {
-  uint4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc_addr)
-               : "memory");
-  return v;
-}
-
-__device__ __forceinline__ void multimem_st16(void* mc_addr, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
-               "r"(v.z), "r"(v.w)
-               : "memory");
-}
-
-// Remote part of one unit: the W copies (peer loads) or the switch-reduced copy
-// (multimem) are requested here and only consumed by peer_sum(), so a thread can
-// have the loads of several units in flight.  `off` is the byte offset of the
-// unit inside every rank's buffer; kPeers bounds the world size at compile time.
-template <typename T, int kPeers>
-__device__ __forceinline__ void peer_load(const FoCommArgs& A, int64_t off, int cnt, bool vec,
-                                          Raw8<T> (&r)[kPeers]) {
-  if (cnt <= 0) return;
-  if (vec && A.multicast != nullptr) {
-    const char* a = static_cast<const char*>(A.multicast) + off;
-    if constexpr (sizeof(T) == 4) {
-      r[0].v = multimem_ld_reduce_f32x4(a);
-      r[0].w = multimem_ld_reduce_f32x4(a + 16);
-    } else if constexpr (Elem<T>::kMant == 7) {
-      r[0].v = multimem_ld_reduce_bf16x8(a);
-    } else {
-      r[0].v = multimem_ld_reduce_f16x8(a);
-    }
-    return;
-  }
-#pragma unroll
-  for (int p = 0; p < kPeers; ++p) {
-    if (p < A.world) {
-      const T* src = reinterpret_cast<const T*>(static_cast<const char*>(A.grad[p]) + off);
-      r[p].v = make_uint4(0, 0, 0, 0);
-      if constexpr (sizeof(T) == 4) r[p].w = make_uint4(0, 0, 0, 0);
-      if (vec) load_raw8<T>(r[p], src, true);
-      else load_raw8_partial<T>(r[p], src, cnt);
-    }
-  }
-}
-// Sum in fp32, in rank order (every replica adds in the same order).
-template <typename T, int kPeers>
-__device__ __forceinline__ void peer_sum(const FoCommArgs& A, int cnt, bool vec, const Raw8<T> (&r)[kPeers],
-                                         float2 (&g)[4]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) g[i] = make_float2(0.f, 0.f);
-  if (cnt <= 0) return;
-  if (vec && A.multicast != nullptr) {
-    unpack8<T>(r[0], g);
-    return;
-  }
-#pragma unroll
-  for (int p = 0; p < kPeers; ++p) {
-    if (p < A.world) {
-      float2 x[4];
-      unpack8<T>(r[p], x);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) g[i] = add2(g[i], x[i]);
-    }
-  }
-}
-template <typename T>
-__device__ __forceinline__ void reduce_unit(const FoCommArgs& A, int64_t off, int cnt, bool vec,
-                                            float2 (&g)[4]) {
-  Raw8<T> r[FO_MAX_PEERS];
-  peer_load<T, FO_MAX_PEERS>(A, off, cnt, vec, r);
-  peer_sum<T, FO_MAX_PEERS>(A, cnt, vec, r, g);
-}
-
-struct CommWalker {
-  const FoSeg* segs;
-  const int32_t* cb;
-  int seg, seg_begin, seg_end;
-  FoSeg S;
-  bool vec;
-  __device__ __forceinline__ CommWalker(const FoSeg* s, const int32_t* c) : segs(s), cb(c), seg(0) {
-    seg_begin = cb[0];
-    seg_end = cb[1];
-    S = segs[0];
-    vec = vector_safe();
-  }
-  // S.g holds a byte offset into the symmetric buffers here, not a pointer
-  __device__ __forceinline__ bool vector_safe() const {
-    uintptr_t a = reinterpret_cast<uintptr_t>(S.p) | reinterpret_cast<uintptr_t>(S.g) |
-                  reinterpret_cast<uintptr_t>(S.ecc) | reinterpret_cast<uintptr_t>(S.s0) |
-                  reinterpret_cast<uintptr_t>(S.s1);
-    return (a & 15) == 0;
-  }
-  __device__ __forceinline__ void seek(int c) {
-    if (c >= seg_end) {
-      do { ++seg; } while (c >= cb[seg + 1]);
-      S = segs[seg];
-      seg_begin = cb[seg];
-      seg_end = cb[seg + 1];
-      vec = vector_safe();
-    }
-  }
-};
-
-// Writes the averaged gradient of one unit to `grad_out` (optional).
-template <typename T>
-__device__ __forceinline__ void store_grad_out(const FoCommArgs& A, int64_t goff, int cnt, bool vec,
-                                               const float2 (&g)[4], float scale) {
-  if (A.grad_out == nullptr || cnt <= 0) return;
-  float2 s[4], back[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) s[i] = mul2(g[i], splat2(scale));
-  Raw8<T> r;
-  pack8<T>(s, r, back);
-  T* dst = reinterpret_cast<T*>(static_cast<char*>(A.grad_out) + (goff - A.grad_out_sub));
-  const bool v = vec && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-  store_raw8<T>(r, dst, cnt, v);
-}
-
-// All-gather on write: the freshly narrowed parameter unit goes to the same offset of
-// every rank's parameter buffer (W peer stores, or one multimem.st replicated by the switch).
-template <typename T, int kPeers>
-__device__ __forceinline__ void push_param(const FoCommArgs& A, int64_t off, int cnt, bool vec,
-                                           const Raw8<T>& pn) {
-  if (cnt <= 0) return;
-  off += A.param_out_delta;
-  if (vec && A.param_out_mc != nullptr && (off & 15) == 0) {
-    char* d = static_cast<char*>(A.param_out_mc) + off;
-    multimem_st16(d, pn.v);
-    if constexpr (sizeof(T) == 4) multimem_st16(d + 16, pn.w);
-    return;
-  }
-#pragma unroll
-  for (int p = 0; p < kPeers; ++p) {
-    if (p < A.world) {
-      T* d = reinterpret_cast<T*>(static_cast<char*>(A.param_out[p]) + off);
-      const bool v = vec && ((reinterpret_cast<uintptr_t>(d) & 15) == 0);
-      store_raw8<T>(pn, d, cnt, v);
-    }
-  }
-}
-
-// Units per thread by world size: the fewer ranks, the fewer remote loads one unit
-// issues, so more units are put in flight per thread (2 ranks: 4 units, 3-4 ranks: 2,
-// 5-8 ranks: 1); remote requests in flight per thread stay at 8 x 16 bytes.
-template <int kU>
+// Units per thread and remote copies per unit.  With peer loads a unit issues one 16-byte
+// request per rank, so the fewer ranks, the more units a thread puts in flight (2 ranks: 4
+// units, 3-4 ranks: 2, 5-8 ranks: 1; eight requests per thread either way).  With
+// multimem.ld_reduce a unit is ONE request whatever the world size (the switch adds the
+// ranks' copies), so a thread always takes 4 units: the kernel is bound by NVLink latency
+// times bytes in flight, and the more a CTA keeps in flight, the fewer CTAs (SMs taken
+// from backward's GEMMs) saturate the links.
+template <int kU, bool kMc>
 struct PeerCfg {
-  static constexpr int kPeers = FO_MAX_PEERS / kU;
+  static constexpr int kPeers = kMc ? 1 : FO_MAX_PEERS / kU;  // register slots per unit
   static constexpr int kChunk = kCommThreads * kUnit * kU;
-  static constexpr int kCtas = kU == 1 ? kCommCtasPerSm : 2;
+  static constexpr int kCtas = 2;  // 128 registers per thread: no variant of bf16 / fp16 spills
 };
 
-template <typename T, int kErr, int kStates, bool kQ, int kU, typename Hyper, typename Update>
+template <typename T, int kErr, int kStates, bool kQ, int kU, bool kMc, typename Hyper, typename Update>
 __device__ __forceinline__ void peer_step_body(const FoSeg* segs, const int32_t* cb, int total_chunks,
                                                const Hyper& H, const FoCommArgs& A, Update update) {
   using Regs = UnitRegs<T, kErr, kStates, kQ>;
-  constexpr int kPeers = PeerCfg<kU>::kPeers;
+  using Cfg = PeerCfg<kU, kMc>;
+  constexpr int kPeers = Cfg::kPeers;
   CommWalker w(segs, cb);
   for (int c = blockIdx.x; c < total_chunks; c += gridDim.x) {
     w.seek(c);
-    const int64_t chunk_base = (int64_t)(c - w.seg_begin) * PeerCfg<kU>::kChunk;
+    const int64_t chunk_base = (int64_t)(c - w.seg_begin) * Cfg::kChunk;
     const int64_t g0 = (int64_t)reinterpret_cast<intptr_t>(w.S.g);
     Raw8<T> remote[kU][kPeers];
-    int cnt[kU];
+    // phase 1: request the remote copies of every full, aligned unit of this thread
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
       const int64_t base = chunk_base + (int64_t)(u * kCommThreads + threadIdx.x) * kUnit;
-      const int64_t left = w.S.n - base;
-      cnt[u] = left >= kUnit ? kUnit : (int)left;
-      peer_load<T, kPeers>(A, g0 + base * (int64_t)sizeof(T), cnt[u], w.vec && cnt[u] == kUnit, remote[u]);
+      if (w.vec && w.S.n - base >= kUnit) {
+        const int64_t off = g0 + base * (int64_t)sizeof(T);
+        if constexpr (kMc) {
+          const char* a = static_cast<const char*>(A.multicast) + off;
+          if constexpr (sizeof(T) == 4) {
+            remote[u][0].v = multimem_ld_reduce_f32x4(a);
+            remote[u][0].w = multimem_ld_reduce_f32x4(a + 16);
+          } else if constexpr (Elem<T>::kMant == 7) {
+            remote[u][0].v = multimem_ld_reduce_bf16x8(a);
+          } else {
+            remote[u][0].v = multimem_ld_reduce_f16x8(a);
+          }
+        } else {
+#pragma unroll
+          for (int p = 0; p < kPeers; ++p)
+            if (p < A.world)
+              load_raw8<T>(remote[u][p], reinterpret_cast<const T*>(static_cast<const char*>(A.grad[p]) + off), true);
+        }
+      }
     }
+    // phase 2: local state, sum, update, store (and push)
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
       const int64_t base = chunk_base + (int64_t)(u * kCommThreads + threadIdx.x) * kUnit;
+      const int64_t off = g0 + base * (int64_t)sizeof(T);
       Regs r;
       load_unit_state(r, w.S, base, w.vec);
       const bool vec = w.vec && r.cnt == kUnit;
       float2 p[4], g[4], m[4], v[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) m[i] = v[i] = make_float2(0.f, 0.f);
-      peer_sum<T, kPeers>(A, r.cnt, vec, remote[u], g);
-      store_grad_out<T>(A, g0 + base * (int64_t)sizeof(T), r.cnt, vec, g, H.grad_scale);
+      for (int i = 0; i < 4; ++i) g[i] = m[i] = v[i] = make_float2(0.f, 0.f);
+      if (vec) {
+        if constexpr (kMc) {
+          unpack8<T>(remote[u][0], g);
+        } else {
+#pragma unroll
+          for (int q = 0; q < kPeers; ++q) {
+            if (q < A.world) {  // fp32 sum in rank order: every replica adds in the same order
+              float2 x[4];
+              unpack8<T>(remote[u][q], x);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) g[i] = add2(g[i], x[i]);
+            }
+          }
+        }
+      } else if (r.cnt > 0) {
+        reduce_unit_slow<T>(A, off, r.cnt, g);
+      }
+      store_grad_out<T>(A, off, r.cnt, vec, g, H.grad_scale);
       widen_unit(r, p, m, v);
       update(p, g, m, v, H);
       Raw8<T> pn;
       store_unit(r, w.S, base, w.vec, p, m, v, pn);
-      if (A.push) push_param<T, kPeers>(A, g0 + base * (int64_t)sizeof(T), r.cnt, vec, pn);
+      if (A.push) push_param<T, FO_MAX_PEERS>(A, off, r.cnt, vec, pn);
     }
   }
 }
@@ -333,24 +128,42 @@ struct PeerMomentumUpdate {
   }
 };
 
-template <typename T, int kErr, bool kQ, int kU>
-__global__ void __launch_bounds__(kCommThreads, PeerCfg<kU>::kCtas)
+template <typename T, int kErr, bool kQ, int kU, bool kMc>
+__global__ void __launch_bounds__(kCommThreads, PeerCfg<kU, kMc>::kCtas)
     adam_peer_kernel(const FoSeg* __restrict__ segs, const int32_t* __restrict__ cb, int total_chunks,
                      const __grid_constant__ FoAdamHyper H, const __grid_constant__ FoCommArgs A) {
-  if (!start_barrier(A)) return;
-  peer_step_body<T, kErr, 2, kQ, kU>(segs, cb, total_chunks, H, A, PeerAdamUpdate<kQ>());
+  if (!start_barrier(A)) {
+    end_signal(A, 2, false, false);
+    return;
+  }
+  peer_step_body<T, kErr, 2, kQ, kU, kMc>(segs, cb, total_chunks, H, A, PeerAdamUpdate<kQ>());
   end_signal(A);
 }
 
-template <typename T, int kErr, int kMode, int kU>
-__global__ void __launch_bounds__(kCommThreads, PeerCfg<kU>::kCtas)
+template <typename T, int kErr, int kMode, int kU, bool kMc>
+__global__ void __launch_bounds__(kCommThreads, PeerCfg<kU, kMc>::kCtas)
     momentum_peer_kernel(const FoSeg* __restrict__ segs, const int32_t* __restrict__ cb, int total_chunks,
                          const __grid_constant__ FoMomentumHyper H, const __grid_constant__ FoCommArgs A) {
-  if (!start_barrier(A)) return;
+  if (!start_barrier(A)) {
+    end_signal(A, 2, false, false);
+    return;
+  }
   constexpr int kStates = kMode == FO_STATE_NONE ? 0 : 1;
   constexpr bool kQ = kMode == FO_STATE_Q8;
-  peer_step_body<T, kErr, kStates, kQ, kU>(segs, cb, total_chunks, H, A, PeerMomentumUpdate<(kStates > 0)>());
+  peer_step_body<T, kErr, kStates, kQ, kU, kMc>(segs, cb, total_chunks, H, A, PeerMomentumUpdate<(kStates > 0)>());
   end_signal(A);
+}
+
+// One CTA: publish this rank's arrival on the ready channel and wait (bounded) for every
+// rank's.  Launched in front of a step kernel on the same stream, so that the many CTAs of
+// the step kernel find the flags already set instead of occupying SMs while a slower rank
+// is still packing its gradients.
+__global__ void ready_barrier_kernel(const __grid_constant__ FoCommArgs A) {
+  if (threadIdx.x < A.world) {
+    __threadfence_system();
+    st_release_sys(A.pad[threadIdx.x] + A.ready_channel * FO_MAX_PEERS + A.rank, A.epoch);
+    wait_flag(A, A.ready_channel, threadIdx.x, A.epoch);
+  }
 }
 
 // Plain averaged reduce (no update): out[i] = scale * sum_r peer_r[off + i].
@@ -360,7 +173,10 @@ template <typename T>
 __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
     reduce_peer_kernel(int64_t n, int64_t src_off, T* __restrict__ out, float scale,
                        const __grid_constant__ FoCommArgs A) {
-  if (!start_barrier(A)) return;
+  if (!start_barrier(A)) {
+    end_signal(A, 2, false, false);
+    return;
+  }
   const int64_t n_units = (n + kUnit - 1) / kUnit;
   const bool aligned = ((src_off | reinterpret_cast<intptr_t>(out)) & 15) == 0;
   for (int64_t u = (int64_t)blockIdx.x * kCommThreads + threadIdx.x; u < n_units;
@@ -389,7 +205,10 @@ template <typename T>
 __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
     reduce_bcast_peer_kernel(int64_t n, int64_t src_off, int64_t dst_off, float scale,
                              const __grid_constant__ FoCommArgs A) {
-  if (!start_barrier(A)) return;
+  if (!start_barrier(A)) {
+    end_signal(A, 2, true, false);
+    return;
+  }
   // slices are multiples of 8 elements so that every unit of a slice is whole
   const int64_t slice = ((n + (int64_t)A.world * kUnit - 1) / ((int64_t)A.world * kUnit)) * kUnit;
   const int64_t begin = slice * A.rank;
@@ -427,7 +246,10 @@ __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
 // into slot s of its own buffer, for every s != r.  Buffers are symmetric.
 __global__ void __launch_bounds__(kCommThreads, kCommCtasPerSm)
     allgather_pull_kernel(int64_t slot_bytes, const __grid_constant__ FoCommArgs A) {
-  if (!start_barrier(A)) return;
+  if (!start_barrier(A)) {
+    end_signal(A, 3, false, false);
+    return;
+  }
   const int64_t n16 = slot_bytes / 16;  // slots are multiples of 16 bytes (checked by the host)
   for (int s = 0; s < A.world; ++s) {
     if (s == A.rank) continue;
@@ -451,7 +273,10 @@ __global__ void wait_kernel(const __grid_constant__ FoCommArgs A, int channel) {
   if (threadIdx.x < A.world) wait_flag(A, channel, threadIdx.x, A.epoch);
 }
 
-static int units_for_world(int world) { return world <= 2 ? 4 : (world <= 4 ? 2 : 1); }
+static int units_for_world(int world, bool multicast) {
+  if (multicast) return 4;
+  return world <= 2 ? 4 : (world <= 4 ? 2 : 1);
+}
 
 static int comm_grid(int64_t work_ctas, const FoCommArgs* a, int ctas_per_sm = kCommCtasPerSm) {
   int dev = 0, sms = 148;
@@ -467,22 +292,29 @@ static bool args_ok(const FoCommArgs* a) {
   return a && a->world >= 1 && a->world <= FO_MAX_PEERS && a->rank >= 0 && a->rank < a->world && a->status;
 }
 
-template <typename T, int kErr, int kU>
+// The one-CTA barrier in front of a step kernel (see ready_barrier_kernel).
+static void launch_ready_barrier(const FoCommArgs& A, cudaStream_t st) {
+  if (A.world > 1 && !(A.flags & FO_COMM_NO_BARRIER)) ready_barrier_kernel<<<1, 32, 0, st>>>(A);
+}
+
+template <typename T, int kErr, int kU, bool kMc>
 static int launch_adam_peer_q(const FoSeg* s, const int32_t* cb, int total, const FoAdamHyper& H,
                               const FoCommArgs& A, int quantized, cudaStream_t st) {
-  const int grid = comm_grid(total, &A, PeerCfg<kU>::kCtas);
-  if (quantized) adam_peer_kernel<T, kErr, true, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
-  else adam_peer_kernel<T, kErr, false, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+  const int grid = comm_grid(total, &A, PeerCfg<kU, kMc>::kCtas);
+  launch_ready_barrier(A, st);
+  if (quantized) adam_peer_kernel<T, kErr, true, kU, kMc><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+  else adam_peer_kernel<T, kErr, false, kU, kMc><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
   return (int)cudaGetLastError();
 }
 template <typename T, int kErr>
 static int launch_adam_peer_u(const FoSeg* s, const int32_t* cb, int total, const FoAdamHyper& H,
                               const FoCommArgs& A, int quantized, cudaStream_t st) {
-  switch (units_for_world(A.world)) {
-    case 4: return launch_adam_peer_q<T, kErr, 4>(s, cb, total, H, A, quantized, st);
-    case 2: return launch_adam_peer_q<T, kErr, 2>(s, cb, total, H, A, quantized, st);
+  if (A.multicast != nullptr) return launch_adam_peer_q<T, kErr, 4, true>(s, cb, total, H, A, quantized, st);
+  switch (units_for_world(A.world, false)) {
+    case 4: return launch_adam_peer_q<T, kErr, 4, false>(s, cb, total, H, A, quantized, st);
+    case 2: return launch_adam_peer_q<T, kErr, 2, false>(s, cb, total, H, A, quantized, st);
   }
-  return launch_adam_peer_q<T, kErr, 1>(s, cb, total, H, A, quantized, st);
+  return launch_adam_peer_q<T, kErr, 1, false>(s, cb, total, H, A, quantized, st);
 }
 template <typename T>
 static int launch_adam_peer(const FoSeg* s, const int32_t* cb, int total, const FoAdamHyper& H,
@@ -495,32 +327,34 @@ static int launch_adam_peer(const FoSeg* s, const int32_t* cb, int total, const 
   return launch_adam_peer_u<T, 0>(s, cb, total, H, A, quantized, st);
 }
 
-template <typename T, int kErr, int kU>
+template <typename T, int kErr, int kU, bool kMc>
 static int launch_mom_peer_m(const FoSeg* s, const int32_t* cb, int total, const FoMomentumHyper& H,
                              const FoCommArgs& A, int mode, cudaStream_t st) {
-  const int grid = comm_grid(total, &A, PeerCfg<kU>::kCtas);
+  const int grid = comm_grid(total, &A, PeerCfg<kU, kMc>::kCtas);
+  if (mode != FO_STATE_NONE && mode != FO_STATE_Q8 && mode != FO_STATE_FULL) return (int)cudaErrorInvalidValue;
+  launch_ready_barrier(A, st);
   switch (mode) {
     case FO_STATE_NONE:
-      momentum_peer_kernel<T, kErr, FO_STATE_NONE, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+      momentum_peer_kernel<T, kErr, FO_STATE_NONE, kU, kMc><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
       break;
     case FO_STATE_Q8:
-      momentum_peer_kernel<T, kErr, FO_STATE_Q8, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+      momentum_peer_kernel<T, kErr, FO_STATE_Q8, kU, kMc><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
       break;
-    case FO_STATE_FULL:
-      momentum_peer_kernel<T, kErr, FO_STATE_FULL, kU><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
+    default:
+      momentum_peer_kernel<T, kErr, FO_STATE_FULL, kU, kMc><<<grid, kCommThreads, 0, st>>>(s, cb, total, H, A);
       break;
-    default: return (int)cudaErrorInvalidValue;
   }
   return (int)cudaGetLastError();
 }
 template <typename T, int kErr>
 static int launch_mom_peer_u(const FoSeg* s, const int32_t* cb, int total, const FoMomentumHyper& H,
                              const FoCommArgs& A, int mode, cudaStream_t st) {
-  switch (units_for_world(A.world)) {
-    case 4: return launch_mom_peer_m<T, kErr, 4>(s, cb, total, H, A, mode, st);
-    case 2: return launch_mom_peer_m<T, kErr, 2>(s, cb, total, H, A, mode, st);
+  if (A.multicast != nullptr) return launch_mom_peer_m<T, kErr, 4, true>(s, cb, total, H, A, mode, st);
+  switch (units_for_world(A.world, false)) {
+    case 4: return launch_mom_peer_m<T, kErr, 4, false>(s, cb, total, H, A, mode, st);
+    case 2: return launch_mom_peer_m<T, kErr, 2, false>(s, cb, total, H, A, mode, st);
   }
-  return launch_mom_peer_m<T, kErr, 1>(s, cb, total, H, A, mode, st);
+  return launch_mom_peer_m<T, kErr, 1, false>(s, cb, total, H, A, mode, st);
 }
 template <typename T>
 static int launch_mom_peer(const FoSeg* s, const int32_t* cb, int total, const FoMomentumHyper& H,
@@ -535,7 +369,23 @@ static int launch_mom_peer(const FoSeg* s, const int32_t* cb, int total, const F
 
 }  // namespace fo
 
-extern "C" int fo_comm_chunk_elems(int world) { return fo::kCommChunk * fo::units_for_world(world); }
+namespace fo {
+// fo_comm_staged.cu; -1 when the combination is not served by a staged kernel
+int staged_adam_peer_launch(const FoSeg* s, const int32_t* cb, int total, const FoAdamHyper& H,
+                            const FoCommArgs& A, int dtype, int err_bytes, int quantized, cudaStream_t st);
+int staged_momentum_peer_launch(const FoSeg* s, const int32_t* cb, int total, const FoMomentumHyper& H,
+                                const FoCommArgs& A, int dtype, int err_bytes, int state_mode, cudaStream_t st);
+
+static bool use_staged(const FoCommArgs& A, int dtype, int q8_states) {
+  return A.variant == 1 && A.multicast == nullptr && q8_states && (dtype == FO_BF16 || dtype == FO_FP16);
+}
+}  // namespace fo
+
+extern "C" int fo_comm_step_chunk_elems(const FoCommArgs* comm, int dtype, int q8_states) {
+  if (!comm) return fo::kCommChunk;
+  if (fo::use_staged(*comm, dtype, q8_states)) return fo::kCommChunk;  // 2048: one unit per consumer thread
+  return fo::kCommChunk * fo::units_for_world(comm->world, comm->multicast != nullptr);
+}
 
 extern "C" int fo_adam_step_peer(const FoSeg* segs, const int32_t* chunk_begin, int n_seg, int total_chunks,
                                  int dtype, int err_bytes, int quantized, const FoAdamHyper* hyper,
@@ -543,6 +393,11 @@ extern "C" int fo_adam_step_peer(const FoSeg* segs, const int32_t* chunk_begin, 
   if (!fo::args_ok(comm) || !hyper) return (int)cudaErrorInvalidValue;
   if (n_seg <= 0 || total_chunks <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (fo::use_staged(*comm, dtype, quantized)) {
+    fo::launch_ready_barrier(*comm, st);
+    return fo::staged_adam_peer_launch(segs, chunk_begin, total_chunks, *hyper, *comm, dtype, err_bytes, quantized,
+                                       st);
+  }
   switch (dtype) {
     case FO_BF16:
       return fo::launch_adam_peer<__nv_bfloat16>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes,
@@ -561,6 +416,11 @@ extern "C" int fo_momentum_step_peer(const FoSeg* segs, const int32_t* chunk_beg
   if (!fo::args_ok(comm) || !hyper) return (int)cudaErrorInvalidValue;
   if (n_seg <= 0 || total_chunks <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (fo::use_staged(*comm, dtype, state_mode == FO_STATE_Q8)) {
+    fo::launch_ready_barrier(*comm, st);
+    return fo::staged_momentum_peer_launch(segs, chunk_begin, total_chunks, *hyper, *comm, dtype, err_bytes,
+                                           state_mode, st);
+  }
   switch (dtype) {
     case FO_BF16:
       return fo::launch_mom_peer<__nv_bfloat16>(segs, chunk_begin, total_chunks, *hyper, *comm, err_bytes,
@@ -638,4 +498,16 @@ extern "C" int fo_comm_wait(const FoCommArgs* comm, int channel, void* stream) {
   if (!fo::args_ok(comm)) return (int)cudaErrorInvalidValue;
   fo::wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(*comm, channel);
   return (int)cudaGetLastError();
+}
+
+extern "C" int fo_comm_barrier(const FoCommArgs* comm, void* stream) {
+  if (!fo::args_ok(comm)) return (int)cudaErrorInvalidValue;
+  fo::ready_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(*comm);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fo_memcpy_async(void* dst, const void* src, int64_t nbytes, void* stream) {
+  if (nbytes < 0 || (nbytes > 0 && (!dst || !src))) return (int)cudaErrorInvalidValue;
+  if (nbytes == 0) return 0;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)nbytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
 }

@@ -53,6 +53,22 @@ __global__ void __launch_bounds__(kNaThreads, kNaCtasPerSm)
   }
 }
 
+// The table is written by small kernels that carry the segments in their launch parameters:
+// the driver copies launch parameters when the launch is issued, so the caller's `segs`
+// array is free again when fo_adam_step_noalloc() returns, whatever kind of host memory it
+// is, and the host never waits for the stream (a cudaMemcpyAsync from pageable memory would
+// make it wait, from pinned memory it would read `segs` later).
+constexpr int kFillSegs = 48;  // 48 * 64 + 49 * 4 + 8 bytes: below the 4 KB of launch parameters
+struct FillArgs {
+  FoSeg segs[kFillSegs];
+  int32_t chunk_begin[kFillSegs + 1];  // chunk_begin[first .. first + count]
+  int first, count;
+};
+__global__ void fill_table_kernel(NoallocTable* table, const __grid_constant__ FillArgs a) {
+  for (int i = threadIdx.x; i < a.count; i += blockDim.x) table->segs[a.first + i] = a.segs[i];
+  for (int i = threadIdx.x; i <= a.count; i += blockDim.x) table->chunk_begin[a.first + i] = a.chunk_begin[i];
+}
+
 // Device address of g_noalloc_table on each device, filled on first use.
 NoallocTable* g_table_addr[kMaxDevices];
 int g_sm_count[kMaxDevices];
@@ -100,17 +116,25 @@ int launch_e(const NoallocTable* t, int total, const FoAdamHyper& H, int err, in
 extern "C" int fo_adam_step_noalloc(const FoSeg* segs, int n_seg, int dtype, int err_bytes, int quantized,
                                     const FoAdamHyper* hyper, void* stream) {
   using namespace fo;
-  if (n_seg == 0) return 0;
   if (segs == nullptr || hyper == nullptr || n_seg < 0) {
     fprintf(stderr, "fo_adam_step_noalloc: null argument or negative segment count\n");
     return FO_NOALLOC_ERR_BAD_ARGUMENT;
   }
+  if (dtype != FO_BF16 && dtype != FO_FP16 && dtype != FO_FP32) {
+    fprintf(stderr, "fo_adam_step_noalloc: unknown dtype code %d\n", dtype);
+    return FO_NOALLOC_ERR_BAD_ARGUMENT;
+  }
+  if (err_bytes < 0 || err_bytes > 2 || (dtype == FO_FP32 && err_bytes != 0)) {
+    fprintf(stderr, "fo_adam_step_noalloc: err_bytes %d is not valid for dtype code %d\n", err_bytes, dtype);
+    return FO_NOALLOC_ERR_BAD_ARGUMENT;
+  }
+  if (n_seg == 0) return 0;
   if (n_seg > FO_NOALLOC_MAX_SEGS) {
     fprintf(stderr, "fo_adam_step_noalloc: %d tensors exceed the built-in table of %d; split the call\n",
             n_seg, (int)FO_NOALLOC_MAX_SEGS);
     return FO_NOALLOC_ERR_TOO_MANY_SEGS;
   }
-  // chunk prefix on the host; 8 KB of stack
+  // chunk prefix on the host; 8 KB of stack.  Everything is validated before the first launch.
   int32_t chunk_begin[FO_NOALLOC_MAX_SEGS + 1];
   int64_t total = 0;
   chunk_begin[0] = 0;
@@ -133,18 +157,21 @@ extern "C" int fo_adam_step_noalloc(const FoSeg* segs, int n_seg, int dtype, int
   int rc = table_for_current_device(&table, &sms);
   if (rc) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaMemcpyAsync(table->segs, segs, sizeof(FoSeg) * (size_t)n_seg, cudaMemcpyHostToDevice, st);
-  if (e != cudaSuccess) return (int)e;
-  e = cudaMemcpyAsync(table->chunk_begin, chunk_begin, sizeof(int32_t) * (size_t)(n_seg + 1),
-                      cudaMemcpyHostToDevice, st);
-  if (e != cudaSuccess) return (int)e;
+  for (int first = 0; first < n_seg; first += kFillSegs) {
+    FillArgs a;
+    a.first = first;
+    a.count = n_seg - first < kFillSegs ? n_seg - first : kFillSegs;
+    for (int i = 0; i < a.count; ++i) a.segs[i] = segs[first + i];
+    for (int i = 0; i <= a.count; ++i) a.chunk_begin[i] = chunk_begin[first + i];
+    fill_table_kernel<<<1, 64, 0, st>>>(table, a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
   int grid = sms * kNaCtasPerSm;
   if (total < grid) grid = (int)total;
   switch (dtype) {
     case FO_BF16: return launch_e<__nv_bfloat16>(table, (int)total, *hyper, err_bytes, quantized, grid, st);
     case FO_FP16: return launch_e<__half>(table, (int)total, *hyper, err_bytes, quantized, grid, st);
-    case FO_FP32: return launch_e<float>(table, (int)total, *hyper, err_bytes, quantized, grid, st);
   }
-  fprintf(stderr, "fo_adam_step_noalloc: unknown dtype code %d\n", dtype);
-  return FO_NOALLOC_ERR_BAD_ARGUMENT;
+  return launch_e<float>(table, (int)total, *hyper, err_bytes, quantized, grid, st);
 }

@@ -27,11 +27,18 @@
 //     that first call before starting any stream capture;
 //   * all calls on a device share the one table.  Each call rewrites the part
 //     it uses before launching (stale entries beyond n_seg are never read, so
-//     nothing needs clearing), and copy + kernel are ordered on `stream`.  Two
-//     calls whose work overlaps on the GPU (different streams, no event
-//     between them) race on the table: serialise them.
-//   * no cudaMalloc, cudaFree or other allocating call is made; `segs` is
-//     ordinary host memory and may be reused as soon as the call returns.
+//     nothing needs clearing); the kernels that write the table and the step
+//     kernel are ordered on `stream`.  Two calls whose work overlaps on the
+//     GPU (different streams, no event between them) race on the table:
+//     serialise them.
+//   * no cudaMalloc, cudaFree, cudaMemcpy or other allocating or synchronising
+//     call is made.  The segments reach the device inside the launch
+//     parameters of small table-writing kernels (48 segments per launch), so
+//     `segs` may be any host memory, pageable or pinned, is read completely
+//     before the call returns and may be reused at once, and the host never
+//     waits for `stream`.
+//   * every argument is validated before the first launch: a refused call has
+//     touched neither the table nor the stream.
 #pragma once
 
 #include "fo_api.h"

@@ -15,6 +15,11 @@ namespace fo {
 
 constexpr int kQThreads = 256;
 
+// Every kernel here gives a thread one unit of 8 consecutive elements per iteration and moves
+// it with 16-byte (8-byte for byte-sized elements) vector accesses when the tensor's base
+// address allows and the unit is whole; tails and unaligned tensors go element by element.
+// The arithmetic per element is the same in both paths.
+
 template <typename T>
 __device__ __forceinline__ float load_as_float(const T* p, int64_t i) {
   if constexpr (sizeof(T) == 4) return p[i];
@@ -22,33 +27,146 @@ __device__ __forceinline__ float load_as_float(const T* p, int64_t i) {
   else return __bfloat162float(p[i]);
 }
 
+template <typename T>
+__device__ __forceinline__ bool aligned_for_units(const T* p) {
+  constexpr uintptr_t need = sizeof(T) * kUnit >= 16 ? 16 : sizeof(T) * kUnit;
+  return (reinterpret_cast<uintptr_t>(p) & (need - 1)) == 0;
+}
+
+// 8 elements of any supported float type -> fp32 (exact widening); zero beyond n.
+template <typename T>
+__device__ __forceinline__ void load8f(const T* p, int64_t base, int64_t n, bool vec, float (&v)[kUnit]) {
+  if (vec && base + kUnit <= n) {
+    if constexpr (sizeof(T) == 4) {
+      const uint4 a = ld16_stream(p + base), b = ld16_stream(p + base + 4);
+      v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
+      v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y); v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+    } else {
+      const uint4 a = ld16_stream(p + base);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (std::is_same<T, __half>::value) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+          v[2 * i] = f.x;
+          v[2 * i + 1] = f.y;
+        } else {
+          v[2 * i] = __uint_as_float(w[i] << 16);
+          v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kUnit; ++i) v[i] = base + i < n ? load_as_float(p, base + i) : 0.0f;
+  }
+}
+// 8 narrow elements, raw 16-bit patterns (for the exponent arithmetic of the correction).
+template <typename T>
+__device__ __forceinline__ void load8bits(const T* p, int64_t base, int64_t n, bool vec, uint16_t (&h)[kUnit]) {
+  static_assert(sizeof(T) == 2, "narrow types only");
+  if (vec && base + kUnit <= n) {
+    const uint4 a = ld16_stream(p + base);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      h[2 * i] = (uint16_t)(w[i] & 0xffffu);
+      h[2 * i + 1] = (uint16_t)(w[i] >> 16);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kUnit; ++i) h[i] = base + i < n ? reinterpret_cast<const uint16_t*>(p)[base + i] : (uint16_t)0;
+  }
+}
+__device__ __forceinline__ void store8f(float* p, int64_t base, int64_t n, bool vec, const float (&v)[kUnit]) {
+  if (vec && base + kUnit <= n) {
+    st16(p + base, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])));
+    st16(p + base + 4,
+         make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7])));
+  } else {
+#pragma unroll
+    for (int i = 0; i < kUnit; ++i)
+      if (base + i < n) p[base + i] = v[i];
+  }
+}
+// 8 one-byte or two-byte integers (two's complement in the low bits of c[i]).
+template <typename E>
+__device__ __forceinline__ void store8i(E* p, int64_t base, int64_t n, bool vec, const int (&c)[kUnit]) {
+  if (vec && base + kUnit <= n) {
+    if constexpr (sizeof(E) == 1) {
+      uint2 o;
+      o.x = (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)(c[3] & 0xff) << 24);
+      o.y = (c[4] & 0xff) | ((c[5] & 0xff) << 8) | ((c[6] & 0xff) << 16) | ((uint32_t)(c[7] & 0xff) << 24);
+      st8(p + base, o);
+    } else {
+      uint4 o;
+      o.x = (c[0] & 0xffff) | ((uint32_t)(c[1] & 0xffff) << 16);
+      o.y = (c[2] & 0xffff) | ((uint32_t)(c[3] & 0xffff) << 16);
+      o.z = (c[4] & 0xffff) | ((uint32_t)(c[5] & 0xffff) << 16);
+      o.w = (c[6] & 0xffff) | ((uint32_t)(c[7] & 0xffff) << 16);
+      st16(p + base, o);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kUnit; ++i)
+      if (base + i < n) p[base + i] = (E)c[i];
+  }
+}
+template <typename E>
+__device__ __forceinline__ void load8i(const E* p, int64_t base, int64_t n, bool vec, int (&c)[kUnit]) {
+  if (vec && base + kUnit <= n) {
+    if constexpr (sizeof(E) == 1) {
+      const uint2 a = ld8_stream(p + base);
+      const uint32_t w[2] = {a.x, a.y};
+#pragma unroll
+      for (int i = 0; i < kUnit; ++i) {
+        const uint32_t b = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+        c[i] = std::is_signed<E>::value ? (int)(int8_t)b : (int)b;
+      }
+    } else {
+      const uint4 a = ld16_stream(p + base);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int i = 0; i < kUnit; ++i) c[i] = (int)(int16_t)((w[i >> 1] >> (16 * (i & 1))) & 0xffffu);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kUnit; ++i) c[i] = base + i < n ? (int)p[base + i] : 0;
+  }
+}
+
 // One thread per unit of 8 elements; four lanes form a group.
 template <typename T, bool kSigned, bool kSqrt, bool kSoftsign>
 __global__ void __launch_bounds__(kQThreads) quantize_kernel(const T* __restrict__ x, uint8_t* __restrict__ q,
                                                              __half* __restrict__ scales, int64_t n) {
   const int64_t n_units = ((n + kGroup - 1) / kGroup) * (kGroup / kUnit);
+  const bool vec = aligned_for_units(x) && aligned_for_units(q);
   for (int64_t unit = (int64_t)blockIdx.x * kQThreads + threadIdx.x; unit - threadIdx.x < n_units;
        unit += (int64_t)gridDim.x * kQThreads) {
     const int64_t base = unit * kUnit;
+    const bool live = unit < n_units;
     float v[kUnit];
+    load8f(x, base, live ? n : 0, vec, v);  // zero beyond the tensor: padding cannot raise the absmax
     float a = 0.0f;
 #pragma unroll
     for (int i = 0; i < kUnit; ++i) {
-      float e = (unit < n_units && base + i < n) ? load_as_float(x, base + i) : 0.0f;
-      if (kSqrt) e = __fsqrt_rn(e);
-      v[i] = e;
-      a = fmaxf(a, fabsf(e));
+      if (kSqrt) v[i] = __fsqrt_rn(v[i]);
+      a = fmaxf(a, fabsf(v[i]));
     }
     a = fmaxf(group_max(a), 1e-12f);
     const float qmax = kSigned ? 127.0f : 255.0f;
+    int c[kUnit];
 #pragma unroll
     for (int i = 0; i < kUnit; ++i) {
       float t = __fdiv_rn(v[i], a);
       if (kSoftsign) t = __fdiv_rn(__fmul_rn(t, 2.0f), __fadd_rn(fabsf(t), 1.0f));
-      const float r = floorf(__fadd_rn(__fmul_rn(t, qmax), 0.5f));
-      if (unit < n_units && base + i < n) q[base + i] = kSigned ? (uint8_t)(int8_t)(int)r : (uint8_t)(int)r;
+      c[i] = (int)floorf(__fadd_rn(__fmul_rn(t, qmax), 0.5f));
     }
-    if ((threadIdx.x & 3) == 0 && unit < n_units && base < n) scales[base >> 5] = __float2half_rn(a);
+    if (live) {
+      if (kSigned) store8i(reinterpret_cast<int8_t*>(q), base, n, vec, c);
+      else store8i(q, base, n, vec, c);
+    }
+    if ((threadIdx.x & 3) == 0 && live && base < n) scales[base >> 5] = __float2half_rn(a);
   }
 }
 
@@ -57,22 +175,24 @@ __global__ void __launch_bounds__(kQThreads) dequantize_kernel(const uint8_t* __
                                                                const __half* __restrict__ scales,
                                                                float* __restrict__ out, int64_t n) {
   const int64_t n_units = (n + kUnit - 1) / kUnit;
+  const bool vec = aligned_for_units(q) && aligned_for_units(out);
   for (int64_t unit = (int64_t)blockIdx.x * kQThreads + threadIdx.x; unit < n_units;
        unit += (int64_t)gridDim.x * kQThreads) {
     const int64_t base = unit * kUnit;
     const float sc = __half2float(scales[base >> 5]);
     const float qmax = kSigned ? 127.0f : 255.0f;
+    int c[kUnit];
+    if (kSigned) load8i(reinterpret_cast<const int8_t*>(q), base, n, vec, c);
+    else load8i(q, base, n, vec, c);
+    float r[kUnit];
 #pragma unroll
     for (int i = 0; i < kUnit; ++i) {
-      if (base + i < n) {
-        const float c = kSigned ? (float)(int8_t)q[base + i] : (float)q[base + i];
-        float t = __fdiv_rn(c, qmax);
-        if (kSoftsign) t = __fdiv_rn(t, __fsub_rn(2.0f, fabsf(t)));
-        float r = __fmul_rn(t, sc);
-        if (kSqrt) r = __fmul_rn(r, r);
-        out[base + i] = r;
-      }
+      float t = __fdiv_rn((float)c[i], qmax);
+      if (kSoftsign) t = __fdiv_rn(t, __fsub_rn(2.0f, fabsf(t)));
+      r[i] = __fmul_rn(t, sc);
+      if (kSqrt) r[i] = __fmul_rn(r[i], r[i]);
     }
+    store8f(out, base, n, vec, r);
   }
 }
 
@@ -80,28 +200,42 @@ __global__ void __launch_bounds__(kQThreads) dequantize_kernel(const uint8_t* __
 __device__ __forceinline__ float pow2i(int e) { return __int_as_float((e + 127) << 23); }
 
 template <typename T>
-__device__ __forceinline__ int ecc_log_scale(T w) {
+__device__ __forceinline__ int ecc_log_scale_bits(uint16_t bits) {
   constexpr int M = Elem<T>::kMant;
   constexpr int bias = std::is_same<T, __half>::value ? 15 : 127;
-  uint16_t bits;
-  if constexpr (std::is_same<T, __half>::value) bits = __half_as_ushort(w);
-  else bits = __bfloat16_as_ushort(w);
   const int field = (bits & 0x7FFF) >> M;
   const int e = field == 0 ? 1 - bias : field - bias;
   return e - M - 1;
+}
+template <typename T>
+__device__ __forceinline__ float narrow_bits_to_float(uint16_t bits) {
+  if constexpr (std::is_same<T, __half>::value) return __half2float(__ushort_as_half(bits));
+  else return __uint_as_float((uint32_t)bits << 16);
 }
 
 template <typename T, typename E>
 __global__ void __launch_bounds__(kQThreads) ecc_decode_kernel(const T* __restrict__ w, const E* __restrict__ ecc,
                                                                float* __restrict__ out, int64_t n) {
   const float smax = sizeof(E) == 1 ? 127.0f : 32767.0f;
-  for (int64_t i = (int64_t)blockIdx.x * kQThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kQThreads) {
-    const T wn = w[i];
-    const int ls = ecc_log_scale(wn);
-    const int h = ls >> 1;  // floor(ls / 2)
-    const float corr = __fdiv_rn((float)ecc[i], smax);
-    const float e = __fmul_rn(__fmul_rn(corr, pow2i(h)), pow2i(ls - h));
-    out[i] = __fadd_rn(load_as_float(w, i), e);
+  const int64_t n_units = (n + kUnit - 1) / kUnit;
+  const bool vec = aligned_for_units(w) && aligned_for_units(ecc) && aligned_for_units(out);
+  for (int64_t unit = (int64_t)blockIdx.x * kQThreads + threadIdx.x; unit < n_units;
+       unit += (int64_t)gridDim.x * kQThreads) {
+    const int64_t base = unit * kUnit;
+    uint16_t h[kUnit];
+    int c[kUnit];
+    load8bits(w, base, n, vec, h);
+    load8i(ecc, base, n, vec, c);
+    float r[kUnit];
+#pragma unroll
+    for (int i = 0; i < kUnit; ++i) {
+      const int ls = ecc_log_scale_bits<T>(h[i]);
+      const int hh = ls >> 1;  // floor(ls / 2)
+      const float corr = __fdiv_rn((float)c[i], smax);
+      const float e = __fmul_rn(__fmul_rn(corr, pow2i(hh)), pow2i(ls - hh));
+      r[i] = __fadd_rn(narrow_bits_to_float<T>(h[i]), e);
+    }
+    store8f(out, base, n, vec, r);
   }
 }
 
@@ -109,33 +243,65 @@ template <typename T, typename E>
 __global__ void __launch_bounds__(kQThreads) ecc_encode_kernel(const float* __restrict__ x, const T* __restrict__ w,
                                                                E* __restrict__ ecc, int64_t n) {
   const float smax = sizeof(E) == 1 ? 127.0f : 32767.0f;
-  for (int64_t i = (int64_t)blockIdx.x * kQThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kQThreads) {
-    const T wn = w[i];
-    const int neg = -ecc_log_scale(wn);
-    const int h = neg >> 1;
-    const float e = __fsub_rn(x[i], load_as_float(w, i));
-    float en = __fmul_rn(__fmul_rn(e, pow2i(h)), pow2i(neg - h));
-    en = fminf(fmaxf(en, -1.0f), 1.0f);
-    const float s = __fmul_rn(en, smax);
-    const float r = copysignf(floorf(__fadd_rn(fabsf(s), 0.5f)), s);
-    ecc[i] = (E)(int)r;
+  const int64_t n_units = (n + kUnit - 1) / kUnit;
+  const bool vec = aligned_for_units(x) && aligned_for_units(w) && aligned_for_units(ecc);
+  for (int64_t unit = (int64_t)blockIdx.x * kQThreads + threadIdx.x; unit < n_units;
+       unit += (int64_t)gridDim.x * kQThreads) {
+    const int64_t base = unit * kUnit;
+    uint16_t h[kUnit];
+    float xv[kUnit];
+    load8bits(w, base, n, vec, h);
+    load8f(x, base, n, vec, xv);
+    int c[kUnit];
+#pragma unroll
+    for (int i = 0; i < kUnit; ++i) {
+      const int neg = -ecc_log_scale_bits<T>(h[i]);
+      const int hh = neg >> 1;
+      const float e = __fsub_rn(xv[i], narrow_bits_to_float<T>(h[i]));
+      float en = __fmul_rn(__fmul_rn(e, pow2i(hh)), pow2i(neg - hh));
+      en = fminf(fmaxf(en, -1.0f), 1.0f);
+      const float s = __fmul_rn(en, smax);
+      c[i] = (int)copysignf(floorf(__fadd_rn(fabsf(s), 0.5f)), s);
+    }
+    store8i(ecc, base, n, vec, c);
   }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kQThreads) maxabs_kernel(const T* __restrict__ x, int64_t n, float* out) {
   float a = 0.0f;
-  for (int64_t i = (int64_t)blockIdx.x * kQThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kQThreads)
-    a = fmaxf(a, fabsf(load_as_float(x, i)));
+  const int64_t n_units = (n + kUnit - 1) / kUnit;
+  const bool vec = aligned_for_units(x);
+  for (int64_t unit = (int64_t)blockIdx.x * kQThreads + threadIdx.x; unit < n_units;
+       unit += (int64_t)gridDim.x * kQThreads) {
+    float v[kUnit];
+    load8f(x, unit * kUnit, n, vec, v);
+#pragma unroll
+    for (int i = 0; i < kUnit; ++i) a = fmaxf(a, fabsf(v[i]));
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(kFullMask, a, o));
   // non-negative floats order like their bit patterns; NaN inputs are dropped by fmaxf
   if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(a));
 }
 
-static int blocks_for(int64_t work_items) {
-  int64_t b = (work_items + kQThreads - 1) / kQThreads;
-  const int64_t cap = 148 * 8;
+// Grid: enough CTAs to fill the device several times over (these kernels hide latency by
+// occupancy), never more than the work; the SM count is read once per device.
+static int blocks_for(int64_t units) {
+  static int sms[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int n = 148;
+  if (dev >= 0 && dev < 64) {
+    if (sms[dev] == 0) {
+      int v = 0;
+      if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+      sms[dev] = v;
+    }
+    n = sms[dev];
+  }
+  int64_t b = (units + kQThreads - 1) / kQThreads;
+  const int64_t cap = (int64_t)n * 16;
   if (b > cap) b = cap;
   if (b < 1) b = 1;
   return (int)b;
@@ -205,7 +371,7 @@ extern "C" int fo_ecc_decode(const void* narrow, int dtype, const void* ecc, int
                              int64_t n, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = fo::blocks_for(n);
+  const int grid = fo::blocks_for((n + fo::kUnit - 1) / fo::kUnit);
   if (dtype == FO_BF16 && err_bytes == 1)
     fo::ecc_decode_kernel<<<grid, fo::kQThreads, 0, st>>>((const __nv_bfloat16*)narrow, (const int8_t*)ecc, out, n);
   else if (dtype == FO_BF16 && err_bytes == 2)
@@ -223,7 +389,7 @@ extern "C" int fo_ecc_encode(const float* x, const void* narrow, int dtype, void
                              int64_t n, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = fo::blocks_for(n);
+  const int grid = fo::blocks_for((n + fo::kUnit - 1) / fo::kUnit);
   if (dtype == FO_BF16 && err_bytes == 1)
     fo::ecc_encode_kernel<<<grid, fo::kQThreads, 0, st>>>(x, (const __nv_bfloat16*)narrow, (int8_t*)ecc, n);
   else if (dtype == FO_BF16 && err_bytes == 2)

@@ -16,6 +16,7 @@
 //
 // Every mbarrier wait is bounded (wall clock); a wait that runs out records a
 // code in StepParams.status (when given), and the waiting warp leaves its loop.
+#include "fo_stage.cuh"
 #include "fo_step_table.cuh"
 
 namespace fo {
@@ -38,7 +39,6 @@ constexpr int kConsumerWarps = kConsumerThreads / 32;
 constexpr int kStagedThreads = kConsumerThreads + 32;
 constexpr int kStagedChunk = kConsumerThreads * kUnit;  // must equal kChunk of the table
 static_assert(kStagedChunk == kChunk, "staged kernels share the chunk prefix of the register path");
-constexpr uint64_t kStageWaitNs = 2000000000ull;
 
 template <int kErr, int kStates>
 struct StageLayout {
@@ -52,51 +52,6 @@ struct StageLayout {
   static constexpr int kBytes = kS0 + kStates * (kStagedChunk / kGroup) * 2;
   static constexpr int kStride = (kBytes + 127) / 128 * 128;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint64_t now_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = now_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (now_ns() - t0 > kStageWaitNs) return false;
-  }
-}
-// Untiled bulk copy global -> this CTA's shared memory, completion counted on `bar`.
-__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(dst_smem)),
-               "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
 
 // A chunk goes through the copy engine when it is a full block of a segment whose
 // streams (including the scale vectors) are 16-byte aligned.
@@ -167,8 +122,10 @@ __device__ __forceinline__ void staged_body(const StepParams& P, const Hyper& H,
     w.seek(c);
     const bool staged = chunk_is_staged(w, c);
     const int64_t base = (int64_t)(c - w.seg_begin) * kStagedChunk + (int64_t)threadIdx.x * kUnit;
-    if (!mbar_wait(&full[s], (j / kStages) & 1)) {
-      if (P.status) atomicOr(P.status, 2u);
+    // one verdict per warp: at the deadline lanes may disagree, and the group shuffles in
+    // store_unit need all 32 lanes
+    if (!__all_sync(kFullMask, mbar_wait(&full[s], (j / kStages) & 1))) {
+      if (P.status && lane == 0) atomicOr(P.status, 2u);
       return;
     }
     Regs r;

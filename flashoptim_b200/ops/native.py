@@ -93,7 +93,12 @@ class FoCommArgs(Structure):
         ("param_out_delta", c_int64),
         ("push_epoch", ctypes.c_uint32),
         ("pushed_channel", c_int),
+        ("variant", c_int),
+        ("flags", c_int),
     ]
+
+
+FO_COMM_NO_BARRIER, FO_COMM_NO_SIGNAL, FO_COMM_PUSH_LOCAL = 1, 2, 4
 
 
 class NativeError(RuntimeError):
@@ -133,8 +138,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.fo_ecc_encode.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p]
     lib.fo_maxabs.restype = c_int
     lib.fo_maxabs.argtypes = [c_void_p, c_int, c_int64, c_void_p, c_void_p]
-    lib.fo_comm_chunk_elems.restype = c_int
-    lib.fo_comm_chunk_elems.argtypes = [c_int]
+    lib.fo_comm_step_chunk_elems.restype = c_int
+    lib.fo_comm_step_chunk_elems.argtypes = [POINTER(FoCommArgs), c_int, c_int]
     lib.fo_adam_step_peer.restype = c_int
     lib.fo_adam_step_peer.argtypes = [
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, POINTER(FoAdamHyper), POINTER(FoCommArgs),
@@ -151,10 +156,16 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.fo_reduce_bcast_peer.argtypes = [c_int64, c_int64, c_int64, c_int, c_float, POINTER(FoCommArgs), c_void_p]
     lib.fo_allgather_peer.restype = c_int
     lib.fo_allgather_peer.argtypes = [c_int64, POINTER(FoCommArgs), c_void_p]
+    lib.fo_adam_step_noalloc.restype = c_int
+    lib.fo_adam_step_noalloc.argtypes = [c_void_p, c_int, c_int, c_int, c_int, POINTER(FoAdamHyper), c_void_p]
     lib.fo_comm_signal.restype = c_int
     lib.fo_comm_signal.argtypes = [POINTER(FoCommArgs), c_int, c_void_p]
     lib.fo_comm_wait.restype = c_int
     lib.fo_comm_wait.argtypes = [POINTER(FoCommArgs), c_int, c_void_p]
+    lib.fo_comm_barrier.restype = c_int
+    lib.fo_comm_barrier.argtypes = [POINTER(FoCommArgs), c_void_p]
+    lib.fo_memcpy_async.restype = c_int
+    lib.fo_memcpy_async.argtypes = [c_void_p, c_void_p, c_int64, c_void_p]
 
 
 def load(path: Optional[str] = None) -> ctypes.CDLL:

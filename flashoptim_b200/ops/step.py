@@ -245,7 +245,8 @@ def launch_adam_peer(
     if rows.shape[0] == 0:
         return
     lib = native.load()
-    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(comm.world), force_device=True)
+    chunk = lib.fo_comm_step_chunk_elems(ctypes.byref(comm), native.DTYPE_CODE[dtype], int(quantized))
+    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=chunk, force_device=True)
     h = hyper.to_c()
     with torch.cuda.device(table.device):
         rc = _launch(
@@ -271,7 +272,9 @@ def launch_momentum_peer(
     if rows.shape[0] == 0:
         return
     lib = native.load()
-    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=lib.fo_comm_chunk_elems(comm.world), force_device=True)
+    chunk = lib.fo_comm_step_chunk_elems(ctypes.byref(comm), native.DTYPE_CODE[dtype],
+                                         int(state_mode == native.FO_STATE_Q8))
+    segs, chunks, n_seg, total, _ = table.prepare(rows, chunk=chunk, force_device=True)
     h = hyper.to_c()
     with torch.cuda.device(table.device):
         rc = _launch(

@@ -313,16 +313,17 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         ready.add(id(p))
         p_local = local_tensor(p)
         quantize = hparams.get("quantize", self._quantize)
+        # states start at zero unless a subclass says otherwise; zero states are two memsets,
+        # not a pass of the quantiser over a tensor of zeros
+        zero_init = type(self)._initial_value_for_state_var is FlashOptimizer._initial_value_for_state_var
         for key, spec in self._quantized_state_spec().items():
             if key not in state:
-                state[key] = MaybeQuantizedTensor(
-                    self._initial_value_for_state_var(p_local.detach(), key),
-                    try_quantize=quantize,
-                    signed=spec.signed,
-                    sqrt=spec.sqrt,
-                    softsign=spec.softsign,
-                    storage_dtype=p_local.dtype,
-                )
+                kw = dict(try_quantize=quantize, signed=spec.signed, sqrt=spec.sqrt, softsign=spec.softsign,
+                          storage_dtype=p_local.dtype)
+                if zero_init:
+                    state[key] = MaybeQuantizedTensor.zeros(p_local.detach(), **kw)
+                else:
+                    state[key] = MaybeQuantizedTensor(self._initial_value_for_state_var(p_local.detach(), key), **kw)
         err_bytes = hparams["master_bytewidth"] - oracle.DTYPE_WIDTHS[p.dtype]
         if state.get("error_bits") is None and err_bytes > 0:
             state["error_bits"] = torch.zeros_like(

@@ -63,6 +63,28 @@ class MaybeQuantizedTensor:
         if data is not None:
             self.set_data(data)
 
+    @classmethod
+    def zeros(
+        cls,
+        like: torch.Tensor,
+        try_quantize: bool = True,
+        signed: bool = True,
+        sqrt: bool = False,
+        softsign: bool = True,
+        storage_dtype: torch.dtype = torch.float32,
+    ) -> "MaybeQuantizedTensor":
+        """An all-zero state shaped like ``like`` without running the quantiser: the codes of
+        zeros are zeros, and the scale of an all-zero group, ``float16(max(0, 1e-12))``, is zero
+        as well, so two memsets give exactly what ``set_data(zeros)`` would."""
+        obj = cls(None, try_quantize=try_quantize, signed=signed, sqrt=sqrt, softsign=softsign,
+                  storage_dtype=storage_dtype)
+        if obj._try_quantize:
+            obj._quantized = torch.zeros(like.shape, dtype=torch.int8 if signed else torch.uint8, device=like.device)
+            obj._scales = torch.zeros((like.numel() + 31) // 32, dtype=torch.float16, device=like.device)
+        else:
+            obj._data = torch.zeros(like.shape, dtype=storage_dtype, device=like.device)
+        return obj
+
     # ------------------------------------------------------------------ accessors
     @property
     def data(self) -> torch.Tensor:

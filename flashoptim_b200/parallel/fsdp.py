@@ -83,6 +83,9 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
         self.param_group = param_group  # FSDP2's group object (for settings that can change later)
         self._slot: Optional[PeerGradients] = None
         self.gather: Optional["PushedAllGather"] = None  # receives the updated parameters
+        # the group that backward reduces last has no GEMM left to share the GPU with:
+        # its kernel ignores the grid cap
+        self.full_grid = False
         w = ctx.peers.world
         self.row_numels = [fp.padded_sharded_param_size.numel() for fp in fsdp_params]
         self.input_numel = w * sum(self.row_numels)
@@ -102,8 +105,8 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
         esize = torch.empty((), dtype=dtype).element_size()
         # a user's all-reduce hook post-processes the reduce-scatter output: the update must wait for it
         hooked = getattr(self.param_group, "_all_reduce_hook", None) is not None
-        if (self.supported and not hooked and numel == self.input_numel and dtype == self.dtype
-                and numel * esize <= self.ctx.pool_bytes):
+        if (self.ctx.enabled and self.supported and not hooked and numel == self.input_numel
+                and dtype == self.dtype and numel * esize <= self.ctx.pool_bytes):
             slot = self.ctx.pool.take()
             slot.wait_done()  # every rank is done reading this buffer's previous contents
             self._slot = slot
@@ -136,11 +139,18 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
         slot.grad_out, slot.grad_out_sub = output_tensor, base
         # the all-gather output of this group has the reduce-scatter input's layout (rank r's
         # padded shards at r * row_bytes), so a parameter lands at its gradient's offset
-        slot.push = self.gather.target if (self.gather is not None and esize == self.gather.esize) else None
+        slot.push = self.gather.target if (self.gather is not None and esize == self.gather.esize
+                                           and self.ctx.push_enabled) else None
+        slot.max_ctas = 0 if self.full_grid else None
+        copy_engine = self.ctx.transport == "copy_engine"
         try:
+            if copy_engine:
+                self._pull_rows(slot, row_bytes)
             self.ctx.optimizer.step_from_peers([fp.sharded_param for fp in self.fsdp_params], slot)
+            if copy_engine:
+                self._finish_copy_engine(slot, row_bytes)
         finally:
-            pushed, slot.push = slot.push is not None, None
+            pushed, slot.push, slot.max_ctas, slot.local_rows = slot.push is not None, None, None, None
         if self.gather is not None:
             if pushed:
                 self.gather.mark_pushed()
@@ -148,6 +158,40 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
                 self.gather.invalidate()
         self.ctx.fused_calls += 1
         return None
+
+
+    # ---- copy-engine transport: the bytes cross NVLink in cudaMemcpyAsync copies (no SM), the
+    # update kernel reads local memory only and runs at HBM speed
+    def _pull_rows(self, slot: PeerGradients, row_bytes: int) -> None:
+        """Barrier, then copy row ``rank`` of every other rank's gradient matrix into the local
+        staging matrix; the step kernels are pointed at it."""
+        peers = self.ctx.peers
+        w, r = peers.world, peers.rank
+        slot.epoch += 1
+        args = peers.comm_args(slot.buf, slot.epoch, slot.ready_channel, slot.done_channel)
+        peers.barrier(args)
+        staging = self.ctx.staging.data_ptr()
+        for i in range(1, w):
+            p = (r + i) % w  # every rank starts with a different peer: no link is asked twice at once
+            peers.copy(staging + p * row_bytes, slot.buf.ptrs[p] + r * row_bytes, row_bytes)
+        slot.local_rows = (staging, row_bytes)
+        if slot.push is not None:
+            slot.push.epoch += 1
+
+    def _finish_copy_engine(self, slot: PeerGradients, row_bytes: int) -> None:
+        """After the update: tell the ranks that their gradient buffers are free again, copy
+        this rank's fresh parameter row into every other rank's all-gather buffer and publish it."""
+        peers = self.ctx.peers
+        w, r = peers.world, peers.rank
+        args = peers.comm_args(slot.buf, slot.epoch, slot.ready_channel, slot.done_channel)
+        peers.signal(args, slot.done_channel)
+        t = slot.push
+        if t is not None:
+            mine = t.buf.ptrs[r] + r * row_bytes + t.delta
+            for i in range(1, w):
+                p = (r + i) % w
+                peers.copy(t.buf.ptrs[p] + r * row_bytes + t.delta, mine, row_bytes)
+            peers.signal(peers.comm_args(t.buf, t.epoch, t.channel, t.channel), t.channel)
 
 
 class PeerAllGather(AllGather):  # type: ignore[misc,valid-type]
@@ -260,28 +304,66 @@ def select_push_groups(sizes: list[int], budget_bytes: Optional[int]) -> list[bo
     return out
 
 
+class UnsupportedFSDPInternals(RuntimeError):
+    """The installed PyTorch does not have the FSDP2 internals this module reads."""
+
+
+# FSDP2 attributes outside its public API that the fused path depends on.  They are checked
+# once, by name, before anything is installed; a PyTorch release that renames one makes
+# enable_fused_fsdp() warn and leave the model on FSDP2's own (NCCL) collectives.
+_PARAM_GROUP_ATTRS = ("fsdp_params", "device", "_reduce_scatter_process_group", "_all_reduce_hook", "_is_hsdp")
+_FSDP_PARAM_ATTRS = ("sharded_param", "padded_sharded_param_size", "fsdp_placement", "offload_to_cpu")
+
+
+def _fsdp_param_groups(model: nn.Module) -> list:
+    """``(module, FSDPParamGroup)`` of every fully_shard-ed module that owns parameters."""
+    if FSDPModule is None:
+        raise UnsupportedFSDPInternals("torch.distributed.fsdp.FSDPModule with custom collectives needs torch >= 2.8")
+    modules = [m for m in model.modules() if isinstance(m, FSDPModule)]
+    if not modules:
+        raise ValueError("model has no fully_shard-ed modules")
+    for name in ("set_custom_reduce_scatter", "set_custom_all_gather", "_get_fsdp_state"):
+        if not hasattr(modules[0], name):
+            raise UnsupportedFSDPInternals(f"FSDPModule.{name} is missing in torch {torch.__version__}")
+    groups = []
+    for m in modules:
+        state = m._get_fsdp_state()
+        if not hasattr(state, "_fsdp_param_group"):
+            raise UnsupportedFSDPInternals(f"FSDPState._fsdp_param_group is missing in torch {torch.__version__}")
+        pg = state._fsdp_param_group
+        if pg is None or not getattr(pg, "fsdp_params", None):
+            continue
+        missing = [a for a in _PARAM_GROUP_ATTRS if not hasattr(pg, a)]
+        missing += [a for a in _FSDP_PARAM_ATTRS if not hasattr(pg.fsdp_params[0], a)]
+        if missing:
+            raise UnsupportedFSDPInternals(
+                f"FSDP2 internals {missing} are missing in torch {torch.__version__}")
+        groups.append((m, pg))
+    return groups
+
+
 class FusedFSDPState:
     def __init__(self, model: nn.Module, optimizer: FlashOptimizer, group, timeout_s, use_multicast, depth,
-                 max_ctas=0, own_all_gather=False, push_params=False, push_budget_bytes=None):
+                 max_ctas=0, own_all_gather=False, push_params=False, push_budget_bytes=None,
+                 last_group_full_grid=True, staged=False, push_multicast=None, transport="kernel"):
         self.optimizer = optimizer
-        modules = [m for m in model.modules() if FSDPModule is not None and isinstance(m, FSDPModule)]
-        if not modules:
-            raise ValueError("model has no fully_shard-ed modules")
-        groups = []
-        for m in modules:
-            pg = m._get_fsdp_state()._fsdp_param_group
-            if pg is not None and pg.fsdp_params:
-                groups.append((m, pg))
+        if transport not in ("kernel", "copy_engine"):
+            raise ValueError(f"transport must be 'kernel' or 'copy_engine', got {transport!r}")
+        self.transport = transport  # may be switched between steps (for comparisons)
+        self.enabled = True        # False: every reduce-scatter goes to NCCL (for comparisons)
+        self.push_enabled = True   # False: updates stop pushing, all-gathers go back to NCCL
+        groups = _fsdp_param_groups(model)
         if not groups:
             raise ValueError("no FSDP parameter groups found")
-        if any(getattr(pg, "_is_hsdp", False) for _, pg in groups):
+        if any(pg._is_hsdp for _, pg in groups):
             # FSDP2 all-reduces the reduce-scatter output across replicas afterwards; an update
             # inside the reduce-scatter would use a gradient that is averaged over one replica only
             raise ValueError("the fused FSDP2 path does not support HSDP (replicate x shard) meshes; "
                              "use fully_shard with optimizer.step() there")
         mesh_group = groups[0][1]._reduce_scatter_process_group
         self.peers = PeerGroup(group or mesh_group, device=groups[0][1].device, timeout_s=timeout_s,
-                               use_multicast=use_multicast, max_ctas=max_ctas)
+                               use_multicast=use_multicast, max_ctas=max_ctas, push_multicast=push_multicast,
+                               variant=1 if staged else 0)
         self.fused_calls = 0
         self.fallbacks = 0
         self.comms = []
@@ -290,8 +372,13 @@ class FusedFSDPState:
             comm = FusedReduceScatter(self, list(pg.fsdp_params), pg)
             need = max(need, comm.input_numel * torch.empty((), dtype=comm.dtype).element_size())
             self.comms.append((m, comm))
+        # modules() lists the outermost module first; its group holds what the model applies
+        # first and is therefore the one whose gradients backward completes last
+        if last_group_full_grid and len(self.comms) > 1:
+            self.comms[0][1].full_grid = True
         self.pool_bytes = need
         self.pool = _Pool(self.peers, need, depth)
+        self._staging: Optional[torch.Tensor] = None
         self.ag_calls = 0
         self.ag_fallbacks = 0
         self.ag_eliminated = 0
@@ -336,6 +423,15 @@ class FusedFSDPState:
         self._installs = installs
         self._listener = on_local_update if push_params else None
 
+    @property
+    def staging(self) -> torch.Tensor:
+        """Copy-engine transport: the local ``[world, row]`` matrix that the peers' gradient rows
+        are copied into (allocated on first use; one buffer serves every group because copies
+        and kernels of consecutive groups are ordered on the reduce-scatter stream)."""
+        if self._staging is None:
+            self._staging = torch.empty(self.pool_bytes, dtype=torch.uint8, device=self.peers.device)
+        return self._staging
+
     def remove(self) -> None:
         """Hand the model back to FSDP2's own collectives (collective: call on every rank,
         between steps).  The symmetric buffers live until this object is dropped."""
@@ -371,6 +467,10 @@ def enable_fused_fsdp(
     own_all_gather: bool = False,
     push_params: bool = False,
     push_budget_bytes: Optional[int] = None,
+    last_group_full_grid: bool = True,
+    staged: bool = False,
+    push_multicast: Optional[bool] = None,
+    transport: str = "kernel",
 ) -> Optional[FusedFSDPState]:
     """Fuse FSDP2's gradient reduce-scatter with ``optimizer``'s sharded update.
 
@@ -386,10 +486,23 @@ def enable_fused_fsdp(
     micro-batch (a second synchronised backward before ``step()`` raises).
     ``depth`` symmetric buffers of the largest group's gradient size are kept.
     ``max_ctas`` caps the kernel's grid: the reduce-scatter is NVLink-bound, so a few
-    dozen CTAs keep the links busy while the SMs stay with backward's GEMMs.
+    dozen CTAs keep the links busy while the SMs stay with backward's GEMMs.  With
+    ``last_group_full_grid`` the outermost module's group, which backward reduces last with no
+    GEMM left to overlap, ignores the cap.
     ``use_multicast`` fetches each unit with one ``multimem.ld_reduce`` (the NVSwitch
     adds the ranks' copies and returns the sum narrowed to the gradient dtype, 1/world
     of the inbound traffic of peer loads) instead of ``world`` peer loads summed in fp32.
+    ``staged`` (peer loads only) runs the bulk-copy staged kernels: a producer thread per CTA
+    streams the ranks' gradient chunks through shared memory with ``cp.async.bulk``, so two or
+    three dozen CTAs (``max_ctas``) saturate NVLink.  ``push_multicast`` chooses ``multimem.st``
+    for the parameter push independently of how gradients are fetched (default: as
+    ``use_multicast``).
+    ``transport="copy_engine"`` moves the bytes differently: after a one-CTA barrier the other
+    ranks' gradient rows are fetched with ``cudaMemcpyAsync`` (the copy engines drive NVLink, no
+    SM takes part), the update kernel then reads only local memory at HBM speed, and the fresh
+    parameters go to the peers' all-gather buffers in further copy-engine copies.  It costs one
+    more pass of the gradients through HBM and one local ``[world, shard]`` staging buffer, and
+    leaves every SM to backward's GEMMs while the links are busy.
     ``own_all_gather`` also replaces FSDP2's parameter all-gather by this library's
     pull kernel over symmetric buffers (:class:`PeerAllGather`).
     ``push_params`` instead removes that all-gather: the update kernel stores the new
@@ -404,7 +517,14 @@ def enable_fused_fsdp(
     state, error = None, None
     try:
         state = FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas, own_all_gather,
-                               push_params, push_budget_bytes)
+                               push_params, push_budget_bytes, last_group_full_grid, staged, push_multicast, transport)
+    except UnsupportedFSDPInternals as e:
+        # same PyTorch on every rank, so every rank lands here together, before any collective
+        import warnings
+
+        warnings.warn(f"fused FSDP2 collectives are not available ({e}); the model stays on FSDP2's own "
+                      "NCCL collectives and optimizer.step()", stacklevel=2)
+        return None
     except (ValueError, TypeError):
         raise  # wrong use, raised before any collective and identically on every rank
     except Exception as e:  # e.g. an allocation that failed on this rank only

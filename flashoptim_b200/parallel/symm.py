@@ -71,6 +71,8 @@ class PeerGroup:
         timeout_s: float = 2.0,
         use_multicast: bool = True,
         max_ctas: int = 0,
+        push_multicast: Optional[bool] = None,
+        variant: int = 0,
     ):
         self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
         self.world = dist.get_world_size(self.group) if self.group is not None else 1
@@ -79,7 +81,13 @@ class PeerGroup:
             raise ValueError(f"at most {native.FO_MAX_PEERS} ranks (one NVSwitch node) are supported")
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.timeout_ns = int(timeout_s * 1e9)
+        # gradients through multimem.ld_reduce (NVSwitch adds the ranks' copies) instead of peer loads
         self.use_multicast = use_multicast
+        # parameter pushes through multimem.st (one store, replicated by the switch) instead of
+        # one store per rank; None: as use_multicast
+        self.push_multicast = use_multicast if push_multicast is None else push_multicast
+        # 1: bulk-copy staged step kernels where they apply (peer loads, 8-bit states, bf16/fp16)
+        self.variant = variant
         self.max_ctas = max_ctas  # grid cap of the peer kernels (0: fill the GPU)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._pad = self.allocate(CHANNELS * native.FO_MAX_PEERS * 4, zero=True)
@@ -100,7 +108,9 @@ class PeerGroup:
         if zero:
             t.zero_()
         hdl = symm_mem.rendezvous(t, group=self.group)
-        mc = int(hdl.multicast_ptr) if (self.use_multicast and hdl.has_multicast_support) else 0
+        # the mapping is recorded whenever the machine has one; use_multicast / push_multicast
+        # decide per launch whether a kernel gets it
+        mc = int(hdl.multicast_ptr) if hdl.has_multicast_support else 0
         buf = SymmBuffer(t, [int(p) for p in hdl.buffer_ptrs], mc, hdl)
         if zero:
             torch.cuda.synchronize(self.device)
@@ -157,6 +167,7 @@ class PeerGroup:
         a.ready_channel = ready_channel
         a.done_channel = done_channel
         a.max_ctas = self.max_ctas
+        a.variant = self.variant
         return a
 
     # ------------------------------------------------------------------ flags
@@ -168,6 +179,18 @@ class PeerGroup:
     def signal(self, args: native.FoCommArgs, channel: int) -> None:
         native.check(native.load().fo_comm_signal(ctypes.byref(args), channel, native.stream_ptr(self.device)),
                      "fo_comm_signal")
+
+    def barrier(self, args: native.FoCommArgs) -> None:
+        """Enqueue a one-CTA kernel that publishes ``args.epoch`` on the ready channel and waits
+        (bounded) for every rank's."""
+        native.check(native.load().fo_comm_barrier(ctypes.byref(args), native.stream_ptr(self.device)),
+                     "fo_comm_barrier")
+
+    def copy(self, dst_ptr: int, src_ptr: int, nbytes: int) -> None:
+        """Enqueue a device-to-device copy between two mapped addresses (either may be another
+        rank's symmetric buffer): the driver's copy engines move the bytes, no SM does."""
+        native.check(native.load().fo_memcpy_async(dst_ptr, src_ptr, nbytes, native.stream_ptr(self.device)),
+                     "fo_memcpy_async")
 
     def poll_status(self) -> None:
         """Like :meth:`check_status` but never waits for the device: each call inspects the copy
@@ -234,19 +257,37 @@ class PeerGradients:
     key: int = 0
     epoch: int = 0  # last epoch used on this buffer
     push: Optional[ParamPush] = None  # step kernels also send the new parameters there
+    max_ctas: Optional[int] = None  # grid cap of the next launch (None: the group's)
+    # Copy-engine transport: the other ranks' rows were copied into this local [world, row_bytes]
+    # buffer beforehand (its address, and the size of a row), so the step kernels read local
+    # memory, synchronise with nobody and publish nothing; next_args() then leaves the epochs alone
+    local_rows: Optional[tuple[int, int]] = None
 
     def next_args(self) -> native.FoCommArgs:
-        self.epoch += 1
+        staged_locally = self.local_rows is not None
+        if not staged_locally:
+            self.epoch += 1
         a = self.group.comm_args(
             self.buf, self.epoch, self.ready_channel, self.done_channel, self.grad_out, self.grad_out_sub
         )
+        if self.max_ctas is not None:
+            a.max_ctas = self.max_ctas
+        if staged_locally:
+            base, row_bytes = self.local_rows
+            for r in range(a.world):
+                if r != a.rank:  # the kernel adds (rank * row_bytes + offset in the row) to every base
+                    a.grad[r] = base + (r - a.rank) * row_bytes
+            a.multicast = None
+            a.flags = native.FO_COMM_NO_BARRIER | native.FO_COMM_NO_SIGNAL | native.FO_COMM_PUSH_LOCAL
         if self.push is not None:
             t = self.push
-            t.epoch += 1
+            if not staged_locally:
+                t.epoch += 1
             a.push = 1
             for r in range(a.world):
                 a.param_out[r] = t.buf.ptrs[r]
-            a.param_out_mc = t.buf.multicast_ptr if (a.multicast and t.buf.multicast_ptr) else None
+            a.param_out_mc = (t.buf.multicast_ptr
+                              if (getattr(self.group, "push_multicast", False) and t.buf.multicast_ptr) else None)
             a.param_out_delta = t.delta
             a.push_epoch = t.epoch & 0xFFFFFFFF
             a.pushed_channel = t.channel

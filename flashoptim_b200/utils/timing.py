@@ -11,6 +11,8 @@ from __future__ import annotations
 import contextlib
 import json
 import os
+import statistics
+import threading
 from dataclasses import dataclass
 from typing import Callable, Optional
 
@@ -60,18 +62,84 @@ def step_bytes_per_element(n_states: int, err_bytes: int, param_bytes: int = 2, 
     return 3 * param_bytes + 2 * n_states * state + 2 * err_bytes
 
 
+FALLBACK_HBM_GBS = 6650.0  # an earlier copy-bandwidth measurement on B200, used when none is given
+
+
 @dataclass
 class Roofline:
     hbm_gbs: float
     source: str  # "measured" | "fallback"
 
     @classmethod
-    def load(cls, repo_root: Optional[str] = None) -> "Roofline":
-        root = repo_root or os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-        path = os.path.join(root, "MEASURED_PEAKS.json")
-        if os.path.exists(path):
-            return cls(float(json.load(open(path))["hbm_gbs"]), "measured")
-        return cls(6650.0, "fallback")
+    def load(cls, peaks_file: Optional[str] = None) -> "Roofline":
+        """Copy bandwidth from a JSON file with an ``hbm_gbs`` entry (``peaks_file``, else the
+        file named by the environment variable ``FLASHOPTIM_B200_PEAKS``); without one the
+        fallback figure, labelled as such."""
+        path = peaks_file or os.environ.get("FLASHOPTIM_B200_PEAKS")
+        if path and os.path.exists(path):
+            with open(path) as f:
+                return cls(float(json.load(f)["hbm_gbs"]), "measured")
+        return cls(FALLBACK_HBM_GBS, "fallback")
 
     def fraction(self, n_elements: int, bytes_per_element: float, ms: float) -> float:
         return n_elements * bytes_per_element / (ms * 1e-3) / 1e9 / self.hbm_gbs
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML every 200 ms from a
+    background thread.  Read-only: no clock, power or mode setting is ever changed."""
+
+    def __init__(self, index: int):
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self):
+        if self._nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }

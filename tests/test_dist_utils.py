@@ -1,5 +1,5 @@
-"""The spawn helper itself: failures surface with every rank's message, and the optional
-second attempt reports the first failure as a warning instead of hiding it."""
+"""The spawn helper itself: failures surface with every rank's message, are never retried,
+and can be written to a file."""
 
 import os
 
@@ -33,10 +33,12 @@ def test_failure_carries_every_ranks_message():
         run_distributed(_raises, world_size=2, backend="gloo")
 
 
-def test_second_attempt_warns_about_the_first_failure(tmp_path):
+def test_a_failure_is_not_repeated_and_is_written_to_a_file(tmp_path, monkeypatch):
     marker = str(tmp_path / "marker")
-    with pytest.warns(UserWarning, match="first attempt fails on rank 0"):
-        run_distributed(_fails_until_marker_exists, world_size=2, backend="gloo", args=(marker,), retries=1)
-    os.remove(marker)
-    with pytest.raises(AssertionError):  # CPU runs are not repeated by default
+    out = tmp_path / "failures"
+    monkeypatch.setenv("FLASHOPTIM_B200_TEST_FAILURE_DIR", str(out))
+    # a second attempt would find the marker and pass: the first failure must stand
+    with pytest.raises(AssertionError, match="first attempt fails on rank 0"):
         run_distributed(_fails_until_marker_exists, world_size=2, backend="gloo", args=(marker,))
+    files = list(out.iterdir())
+    assert len(files) == 1 and "first attempt fails on rank 0" in files[0].read_text()

@@ -17,7 +17,8 @@ class _FakePeers:
     """Stands in for ``PeerGroup``: ordinary host tensors as "symmetric" buffers; waits are
     no-ops because the stand-in kernels below are blocking gloo collectives."""
 
-    def __init__(self, group=None, device=None, timeout_s=2.0, use_multicast=True, max_ctas=0):
+    def __init__(self, group=None, device=None, timeout_s=2.0, use_multicast=True, max_ctas=0,
+                 push_multicast=None, variant=0):
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.device = torch.device("cpu")

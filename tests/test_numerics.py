@@ -218,3 +218,17 @@ def test_master_weight_split_never_hurts_for_any_input(values, dtype, mbw):
     ulp32 = torch.exp2(torch.floor(torch.log2(x.abs().clamp_min(2.0 ** -126))) - 23)
     assert ((r - x).abs() <= (w.float() - x).abs() + ulp32).all()
     assert e.to(torch.int32).abs().max() <= (127 if mbw == 3 else 32767)
+
+
+@pytest.mark.parametrize("signed,sqrt,softsign", [(True, False, True), (False, True, False)])
+def test_zero_state_by_memset_equals_quantised_zeros(signed, sqrt, softsign):
+    from flashoptim_b200.optim.state import MaybeQuantizedTensor
+
+    x = torch.zeros(5, 7)
+    a = MaybeQuantizedTensor(x, signed=signed, sqrt=sqrt, softsign=softsign)
+    b = MaybeQuantizedTensor.zeros(x, signed=signed, sqrt=sqrt, softsign=softsign)
+    assert a.quantized.dtype == b.quantized.dtype and a.quantized.shape == b.quantized.shape
+    assert torch.equal(a.quantized, b.quantized) and torch.equal(a.scales, b.scales)
+    assert torch.equal(a.materialize(), b.materialize())
+    plain = MaybeQuantizedTensor.zeros(x, try_quantize=False, storage_dtype=torch.bfloat16)
+    assert not plain.is_quantized() and plain.data.dtype == torch.bfloat16 and plain.data.shape == x.shape

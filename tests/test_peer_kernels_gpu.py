@@ -49,10 +49,13 @@ def _publish_all(pads, channel, epoch):
         pad[channel * 8: channel * 8 + 8] = epoch
 
 
-@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("variant", [0, 1], ids=["register", "staged"])
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
 @pytest.mark.parametrize("layout", ["ddp", "fsdp"])
-def test_peer_adam_matches_local_step_on_mean_gradient(world, layout):
-    sizes = [4096, 33, 50257, 2048 * 3 + 5]
+def test_peer_adam_matches_local_step_on_mean_gradient(world, layout, variant):
+    # full 2048-element blocks (the staged kernels' bulk copies), tails, a tensor smaller than
+    # a unit group, and enough blocks that a CTA's ring wraps around when the grid is capped
+    sizes = [4096, 33, 50257, 2048 * 3 + 5, 2048 * 40]
     row = sum((n + 7) // 8 * 8 for n in sizes) * 2  # bytes of one rank's (padded) row
     nbytes = row * (world if layout == "fsdp" else 1)
     groups, bufs, pads = _emulated(world, nbytes)
@@ -86,6 +89,8 @@ def test_peer_adam_matches_local_step_on_mean_gradient(world, layout):
                                          decoupled=True, step=h.step))
         _publish_all(pads, 0, 1)  # every other rank has "arrived"
         g = groups[r]
+        g.variant = variant
+        g.max_ctas = 3 if variant else 0  # three CTAs: each walks its ring several times around
         out = torch.zeros(row // 2, dtype=torch.bfloat16, device=DEV)
         buf = SymmBuffer(bufs[r], [b.data_ptr() for b in bufs], 0)
         args = g.comm_args(buf, 1, 0, 1, grad_out=out, grad_out_sub=base, pads=[p.data_ptr() for p in pads])
@@ -132,9 +137,11 @@ def test_peer_adam_matches_local_step_on_mean_gradient(world, layout):
             assert int(pad[0 * 8 + r]) == 1 and int(pad[1 * 8 + r]) == 1
 
 
-def test_peer_momentum_lion_world4():
+@pytest.mark.parametrize("variant", [0, 1], ids=["register", "staged"])
+def test_peer_momentum_lion_world4(variant):
     n, world = 10000, 4
     groups, bufs, pads = _emulated(world, n * 2)
+    groups[1].variant = variant
     gen = torch.Generator(device=DEV).manual_seed(1)
     for b in bufs:
         b.view(torch.bfloat16).copy_(torch.randn(n, device=DEV, generator=gen) * 1e-3)
@@ -212,9 +219,11 @@ def test_two_shot_reduce_broadcast_kernel(n):
         assert torch.equal(got, bufs[0][half:half + n * 2].view(torch.bfloat16).float())
 
 
-def test_wait_that_nothing_satisfies_times_out_and_leaves_state_untouched():
+@pytest.mark.parametrize("variant", [0, 1], ids=["register", "staged"])
+def test_wait_that_nothing_satisfies_times_out_and_leaves_state_untouched(variant):
     world, n = 2, 4096
     groups, bufs, pads = _emulated(world, n * 2, timeout_s=0.05)
+    groups[0].variant = variant
     p, ecc, m, ms, v, vs = _state(n, 9)
     snap = [t.clone() for t in (p, ecc, m, ms, v, vs)]
     buf = SymmBuffer(bufs[0], [b.data_ptr() for b in bufs], 0)
@@ -224,6 +233,8 @@ def test_wait_that_nothing_satisfies_times_out_and_leaves_state_untouched():
     h = AdamHyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1, decoupled=True)
     table = SegmentTable(torch.device(DEV, torch.cuda.current_device()))
     launch_adam_peer(table, rows, torch.bfloat16, 1, True, h, args)
+    torch.cuda.synchronize()
+    assert int(groups[0].status[2]) == 0  # every CTA counted itself out: the counter is back at zero
     with pytest.raises(CommTimeoutError) as ei:
         groups[0].check_status()
     assert "missing rank 1" in str(ei.value)

@@ -71,15 +71,26 @@ def test_noalloc_adam_matches_table_entry_point_twice():
     ref, new = _problem(7), _problem(7)
     dev = torch.device("cuda", torch.cuda.current_device())
     table = SegmentTable(dev)
+    stream = torch.cuda.current_stream().cuda_stream
     for step in (1, 2):
         h = AdamHyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=1e-5, step=step, decoupled=True)
         launch_adam(table, _rows(ref), torch.bfloat16, 1, True, h)
         rows = _rows(new)
         hc = h.to_c()
-        rc = fn(rows.ctypes.data, rows.shape[0], native.FO_BF16, 1, 1, ctypes.byref(hc),
-                torch.cuda.current_stream().cuda_stream)
-        assert rc == 0, rc
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        rc = fn(rows.ctypes.data, rows.shape[0], native.FO_BF16, 1, 1, ctypes.byref(hc), stream)
+        # the caller's array is free again when the call returns, whatever memory it lives in
+        rows[:] = -1
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert rc == 0, rc
+        # the driver's own view of the device: nothing was allocated behind the caller's back.
+        # Checked on the second call: during the first one the driver may still load the
+        # kernels' code onto the device (lazy module loading), which is not an allocation of
+        # this library's and happens once.
+        if step == 2:
+            assert free_after >= free_before, (free_before, free_after)
         _assert_same(ref, new, f"call {step}")
     assert table.uploads >= 1  # the regular path really went through its device table
 
@@ -96,3 +107,31 @@ def test_noalloc_refuses_oversize_requests():
             torch.cuda.current_stream().cuda_stream)
     assert rc == -1
     torch.cuda.synchronize()
+
+
+def test_noalloc_refusals_launch_nothing():
+    """Every refusal happens before the first launch: bad arguments (-3) and more than 2^31
+    chunks (-2) leave the tensors of a valid problem untouched."""
+    fn = _entry()
+    prob = _problem(11)
+    before = [[t.clone() for t in ts] for ts in prob]
+    rows = _rows(prob)
+    h = AdamHyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1, decoupled=True).to_c()
+    stream = torch.cuda.current_stream().cuda_stream
+    n = rows.shape[0]
+    assert fn(rows.ctypes.data, -1, native.FO_BF16, 1, 1, ctypes.byref(h), stream) == -3       # negative count
+    assert fn(None, n, native.FO_BF16, 1, 1, ctypes.byref(h), stream) == -3                     # no segments
+    assert fn(rows.ctypes.data, n, native.FO_BF16, 1, 1, None, stream) == -3                    # no hyper-parameters
+    assert fn(rows.ctypes.data, n, native.FO_BF16, 3, 1, ctypes.byref(h), stream) == -3         # err_bytes 3
+    assert fn(rows.ctypes.data, n, native.FO_FP32, 1, 1, ctypes.byref(h), stream) == -3         # fp32 has no codes
+    assert fn(rows.ctypes.data, n, 7, 1, 1, ctypes.byref(h), stream) == -3                      # unknown dtype
+    neg = rows.copy()
+    neg[3, 7] = -5
+    assert fn(neg.ctypes.data, n, native.FO_BF16, 1, 1, ctypes.byref(h), stream) == -3          # negative length
+    huge = rows.copy()
+    huge[0, 7] = 2 ** 42  # 2^31 chunks of 2048 elements in one tensor
+    assert fn(huge.ctypes.data, n, native.FO_BF16, 1, 1, ctypes.byref(h), stream) == -2
+    torch.cuda.synchronize()
+    for ts, bs in zip(prob, before):
+        for t, b in zip(ts, bs):
+            assert torch.equal(t, b)
