@@ -478,6 +478,8 @@ def main():
             if rank == 0:
                 print(f"[sweep] {results[-1]}", file=sys.stderr, flush=True)
         sampler.stop()
+        if args.timeline:  # the last entry's configuration against FSDP2's NCCL collectives
+            timeline_summary(lambda: train_step(dev_tokens[i % total_steps]), rank, args.timeline, fused_state)
         if rank == 0:
             print(json.dumps({"sweep": results, "n_gpus": world, "steps": args.steps, "model": args.model,
                               "seq_len": s, "optimizer": args.optimizer, "master_weight_bits": mwb,

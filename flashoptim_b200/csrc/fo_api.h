@@ -206,6 +206,15 @@ int fo_comm_barrier(const FoCommArgs* comm, void* stream);
 // driver moves the bytes over NVLink with a copy engine, no SM involved.
 int fo_memcpy_async(void* dst, const void* src, int64_t nbytes, void* stream);
 
+// ---------------------------------------------------------------------------
+// Test support (fo_probe.cu): the fast forms of the master-weight split that the step kernels
+// inline, applied to caller-supplied fp32 values.  n a multiple of 8, pointers 16-byte aligned.
+// ---------------------------------------------------------------------------
+int fo_probe_fast_ecc_split(const float* x, int dtype, int err_bytes, void* narrow, void* ecc, int64_t n,
+                            void* stream);
+int fo_probe_fast_ecc_merge(const void* narrow, int dtype, const void* ecc, int err_bytes, float* out, int64_t n,
+                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,25 +55,16 @@ template <>
 struct Elem<__nv_bfloat16> {
   static constexpr int kMant = 7;
   static constexpr bool kNarrow = true;
-  // Smallest fp32 exponent field for which the correction scale is built from
-  // the value's own exponent.  Below 2^-103 the correction of a bf16 value is
-  // smaller than 2^-111 and is evaluated with this field instead, which keeps
-  // the integer construction of the scale inside the fp32 exponent range.
-  static constexpr uint32_t kMinExpField = 24u << 23;
 };
 template <>
 struct Elem<__half> {
   static constexpr int kMant = 10;
   static constexpr bool kNarrow = true;
-  // fp16 subnormals share the exponent of the smallest normal, 2^-14, whose
-  // fp32 exponent field is 113: clamping there is exact.
-  static constexpr uint32_t kMinExpField = 113u << 23;
 };
 template <>
 struct Elem<float> {
   static constexpr int kMant = 23;
   static constexpr bool kNarrow = false;
-  static constexpr uint32_t kMinExpField = 0;
 };
 
 // 8 consecutive elements of a tensor in registers, raw.
@@ -254,6 +245,12 @@ struct EccConst {
   static constexpr float kEnc = kS / kHalfUlp;
 };
 
+// fp32 exponent field of a narrow value that was widened to fp32, i.e. the bits of 2^E.
+//   bf16: the value's own field.  Zero and bf16 subnormals have field 0, which reads back as
+//         the float 0: on decode their correction (at most 2^-134) is dropped; the encoder
+//         still writes some finite code for them, which no decode ever uses.
+//   fp16: clamped from below at 113, the field of 2^-14: fp16 subnormals (and zero) share the
+//         exponent of the smallest normal, so the clamp is exact.
 template <typename T>
 __device__ __forceinline__ uint32_t exp_field(float w_as_f32) {
   uint32_t f = __float_as_uint(w_as_f32) & 0x7F800000u;

@@ -158,6 +158,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.fo_allgather_peer.argtypes = [c_int64, POINTER(FoCommArgs), c_void_p]
     lib.fo_adam_step_noalloc.restype = c_int
     lib.fo_adam_step_noalloc.argtypes = [c_void_p, c_int, c_int, c_int, c_int, POINTER(FoAdamHyper), c_void_p]
+    lib.fo_probe_fast_ecc_split.restype = c_int
+    lib.fo_probe_fast_ecc_split.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p]
+    lib.fo_probe_fast_ecc_merge.restype = c_int
+    lib.fo_probe_fast_ecc_merge.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p]
     lib.fo_comm_signal.restype = c_int
     lib.fo_comm_signal.argtypes = [POINTER(FoCommArgs), c_int, c_void_p]
     lib.fo_comm_wait.restype = c_int

@@ -75,6 +75,40 @@ def check_kernel_status(device: Optional[torch.device] = None) -> None:
             raise StepKernelError(f"cuda:{idx}: step kernel wait timed out (code {code})")
 
 
+_polls: dict[int, tuple[torch.Tensor, "torch.cuda.Event"]] = {}
+_poll_hosts: dict[int, torch.Tensor] = {}  # one pinned word per device, reused by every poll
+
+
+def poll_kernel_status() -> None:
+    """Non-blocking form of :func:`check_kernel_status`, meant to be called once per step.
+
+    Each call looks at the copy of the status word that the previous call requested (if that
+    copy has arrived) and requests a fresh one on the current stream, so the host never waits
+    for the device.  A bounded wait that ran out inside a step kernel (the warps concerned
+    skipped their chunks, i.e. part of that update is missing) therefore raises
+    :class:`StepKernelError` one or two calls late.  Call :func:`check_kernel_status` where the
+    answer must be current, e.g. before a checkpoint is written."""
+    for idx, t in list(_status.items()):
+        pending = _polls.get(idx)
+        if pending is not None:
+            host, event = pending
+            if not event.query():
+                continue  # still in flight: ask again next time
+            del _polls[idx]
+            code = int(host.item())
+            if code:
+                t.zero_()
+                raise StepKernelError(f"cuda:{idx}: step kernel wait timed out (code {code})")
+        with torch.cuda.device(idx):
+            host = _poll_hosts.get(idx)
+            if host is None:
+                host = _poll_hosts[idx] = torch.empty(1, dtype=torch.int32).pin_memory()
+            host.copy_(t, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+        _polls[idx] = (host, event)
+
+
 def set_step_variant(variant: int) -> None:
     """0: register-path kernels only; 1 (default): bulk-copy staged kernels where they apply."""
     native.load().fo_set_step_variant(int(variant))

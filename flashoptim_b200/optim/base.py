@@ -38,7 +38,7 @@ import torch.nn as nn
 
 from ..ops import oracle
 from ..ops.quant import compute_ecc_bits, maxabs, reconstruct_fp32_param
-from ..ops.step import SegmentTable
+from ..ops.step import SegmentTable, poll_kernel_status
 from .state import MaybeQuantizedTensor, QuantizedTensorSpec
 
 _VALID_MASTER_WEIGHT_BITS = (None, 24, 32)
@@ -148,17 +148,16 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         ):
             if all(p.dtype == torch.float32 for p in all_params):
                 raise ValueError(
-                    f"master_weight_bits={master_weight_bits} has no effect when all "
-                    "parameters are fp32, since fp32 already uses 32 bits. "
-                    "No error correction would be applied in this scenario. "
-                    "Please omit master_weight_bits (or set it to None)."
+                    f"every parameter is float32, so master_weight_bits={master_weight_bits} would add "
+                    "nothing: correction codes exist only for bf16/fp16 parameters. Pass "
+                    "master_weight_bits=None (or set FLASHOPTIM_ALLOW_INEFFECTIVE_MASTER_WEIGHT_BITS=1 "
+                    "to construct the optimizer anyway)."
                 )
         if master_weight_bits is None and any(p.dtype != torch.float32 for p in all_params):
             warnings.warn(
-                "master_weight_bits=None with non-fp32 parameters means pure low-precision "
-                "training (no error correction). Optimizer states will be stored at parameter "
-                "precision. This is numerically fragile, consider setting master_weight_bits=24 "
-                "for stable training.",
+                "bf16/fp16 parameters are being trained without master weights "
+                "(master_weight_bits=None): every update is rounded to the parameter dtype and small "
+                "updates are lost. master_weight_bits=24 adds one byte per parameter and keeps them.",
                 stacklevel=3,
             )
 
@@ -252,10 +251,10 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
                 size = mesh.size(mesh_dim)
                 if param.shape[placement.dim] % size != 0:
                     raise ValueError(
-                        "DCP checkpointing requires evenly-sharded parameters, but parameter "
-                        f"with shape {param.shape} is unevenly sharded on dim {placement.dim} "
-                        f"across {size} ranks. Pad or reshape the parameter so that "
-                        f"shape[{placement.dim}] is divisible by {size}."
+                        f"a parameter of shape {tuple(param.shape)} is split over {size} ranks along "
+                        f"dimension {placement.dim}, which {size} does not divide: its optimizer state "
+                        "cannot be described as an even DTensor shard for torch.distributed.checkpoint. "
+                        f"Make shape[{placement.dim}] a multiple of {size} (pad or reshape)."
                     )
         for key, val in state.items():
             if isinstance(val, torch.Tensor) and not isinstance(val, DTensor) and val.dim() > 0:
@@ -292,14 +291,12 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
         if need > have:
             bits = max(oracle.DTYPE_WIDTHS[p.dtype], master_bytewidth) * 8
             raise NumericsError(
-                f"Learning rate {lr:.3g} yields steps that may be too small to alter the "
-                f"weights for dtype {p.dtype} with master_weight_bits={bits} and weight "
-                f"maximum absolute value {mx} (min step size {2**have:.5g} < resolution "
-                f"{2**need:.5g}). Consider increasing your learning rate, decreasing your "
-                "weight magnitudes, or increasing master_weight_bits. Set "
-                "check_numerics=False to disable this check. If you're getting this error "
-                "after loading a checkpoint, you can call recompute_param_stats() throughout "
-                "training to fail faster and avoid this surprise."
+                f"lr={lr:.3g} is too small for this tensor: its largest weight is {mx:.5g} in "
+                f"{p.dtype} with {bits}-bit master weights, where the smallest representable change "
+                f"is about {2**need:.5g}, but a step moves a weight by about {2**have:.5g}. Raise the "
+                "learning rate, use master_weight_bits=32, or scale the weights down; "
+                "check_numerics=False switches this test off. The weight statistics are cached: "
+                "after loading a checkpoint (or from time to time) recompute_param_stats() refreshes them."
             )
 
     # ------------------------------------------------------------------ state creation
@@ -379,15 +376,15 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
             if p_local.is_cuda and self._fused:
                 if not p_local.is_contiguous():
                     raise RuntimeError(
-                        "FlashOptimizer fused kernels require contiguous parameters, but got "
-                        f"param with shape {p_local.shape} and stride {p_local.stride()}. "
-                        "Call .contiguous() on the parameter or use fused=False."
+                        f"the fused kernels need a contiguous parameter; got shape {tuple(p_local.shape)} "
+                        f"with strides {p_local.stride()}. Make it contiguous or construct the optimizer "
+                        "with fused=False."
                     )
                 if not g_local.is_contiguous():
                     raise RuntimeError(
-                        "FlashOptimizer fused kernels require contiguous gradients, but got "
-                        f"grad with shape {g_local.shape} and stride {g_local.stride()}. "
-                        "Use fused=False for non-contiguous gradients."
+                        f"the fused kernels need a contiguous gradient; got shape {tuple(g_local.shape)} "
+                        f"with strides {g_local.stride()}. Construct the optimizer with fused=False for "
+                        "such gradients."
                     )
                 if g_local.dtype != p_local.dtype:
                     g_local = g_local.to(p_local.dtype)
@@ -418,8 +415,8 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
     def step(self, closure: Optional[Callable] = None) -> Optional[torch.Tensor]:
         if self._gradient_release:
             warnings.warn(
-                "optimizer.step() is a no-op while enable_gradient_release() is active — "
-                "parameters are stepped by gradient hooks.",
+                "gradient release is active: the gradient hooks already update the parameters during "
+                "backward, so optimizer.step() does nothing.",
                 stacklevel=2,
             )
             return None
@@ -431,6 +428,11 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
             self._step_group(group["params"], group, gi)
         for fn in self._post_step_callbacks:
             fn()
+        if self._fused and torch.cuda.is_available():
+            # a bounded wait that ran out inside a step kernel means part of an update is
+            # missing; reported here without waiting for the device, one or two steps late
+            # (ops.step.check_kernel_status() gives the current answer, e.g. before a checkpoint)
+            poll_kernel_status()
         return loss
 
     def _refuse_second_fused_update(self, p: torch.Tensor) -> None:
@@ -507,8 +509,8 @@ class FlashOptimizer(torch.optim.Optimizer, abc.ABC):
     def zero_grad(self, set_to_none: bool = True) -> None:
         if self._gradient_release:
             warnings.warn(
-                "optimizer.zero_grad() is a no-op while enable_gradient_release() is active — "
-                "gradients are freed by gradient hooks.",
+                "gradient release is active: each gradient is freed by its hook right after the "
+                "update, so optimizer.zero_grad() does nothing.",
                 stacklevel=2,
             )
             return

@@ -177,8 +177,8 @@ class MaybeQuantizedTensor:
         if name in d:
             if len(d) != 1:
                 raise ValueError(
-                    f"If state dict specifies {name}, it must not specify other keys. "
-                    f"Got {list(d.keys())}"
+                    f"a checkpoint holds either '{name}' or its compressed pair, not both; found "
+                    f"{sorted(d.keys())}"
                 )
             self.set_data(d[name])
             return

@@ -37,6 +37,37 @@ from ..optim.base import FlashOptimizer
 from .symm import PeerGradients, PeerGroup
 
 
+class ArenaLayout:
+    """Where each gradient bucket of a backward pass goes in the symmetric arena, and what the
+    host has to wait for before the pass overwrites anything.
+
+    Buckets are laid out one after the other in the order DDP hands them over.  DDP rebuilds
+    its buckets after the first iteration, so a region of this pass may overlap several regions
+    of the previous one at other offsets.  The protection therefore does not look at offsets:
+    before the FIRST bucket of a pass is copied in, the stream waits until every rank has
+    published "done" for the LAST kernel of the previous pass.  Epochs grow by one per kernel
+    and a rank's kernels run in order on its side stream, so that one wait covers every region
+    under any layout (and the second half of the arena, which only those kernels' peers write).
+    """
+
+    def __init__(self, half_bytes: int):
+        self.half = half_bytes
+        self.cursor = 0
+
+    def place(self, bucket_index: int, nbytes: int, last_epoch: int) -> tuple[int, int]:
+        """Returns ``(offset, epoch)``: the bucket's byte offset, and the epoch whose "done" flags
+        must be awaited first (0: nothing to wait for)."""
+        wait_epoch = 0
+        if bucket_index == 0:
+            self.cursor = 0
+            wait_epoch = last_epoch
+        off = self.cursor
+        self.cursor += (nbytes + 255) // 256 * 256
+        if self.cursor > self.half:
+            raise RuntimeError("gradient buckets exceed the symmetric arena")
+        return off, wait_epoch
+
+
 class FusedDDPState:
     def __init__(
         self,
@@ -70,8 +101,7 @@ class FusedDDPState:
         ready, done = self.peers.new_channels()
         self.grads = PeerGradients(self.peers, self.arena, ready, done, grad_scale=1.0 / self.peers.world, key=id(self))
         self.side = torch.cuda.Stream(device=params[0].device)
-        self.cursor = 0
-        self.region_epoch: dict[int, int] = {}
+        self.layout = ArenaLayout(self.half)
         self.buckets_fused = 0
         self.buckets_two_shot = 0
         optimizer._post_step_callbacks.append(self._join)
@@ -81,18 +111,12 @@ class FusedDDPState:
 
     def hook(self, _state, bucket):  # no annotations: DDP compares them to the classes themselves
         buf = bucket.buffer()
-        if bucket.index() == 0:
-            self.cursor = 0
         nbytes = buf.numel() * buf.element_size()
-        off = self.cursor
-        self.cursor += (nbytes + 255) // 256 * 256
-        if self.cursor > self.half:
-            raise RuntimeError("gradient buckets exceed the symmetric arena")
+        off, wait_epoch = self.layout.place(bucket.index(), nbytes, self.grads.epoch)
         cur = torch.cuda.current_stream()
-        # peers must have finished reading what this region held in the previous step
-        last = self.region_epoch.get(off, 0)
-        if last and self.peers.world > 1:
-            args = self.peers.comm_args(self.arena, last, self.grads.ready_channel, self.grads.done_channel)
+        # peers must have finished reading what the arena held in the previous pass
+        if wait_epoch and self.peers.world > 1:
+            args = self.peers.comm_args(self.arena, wait_epoch, self.grads.ready_channel, self.grads.done_channel)
             self.peers.wait(args, self.grads.done_channel)
         self.arena.view(off, buf.numel(), buf.dtype).copy_(buf)
         self.side.wait_event(cur.record_event())
@@ -115,7 +139,6 @@ class FusedDDPState:
                 views = [reduced[(g.data_ptr() - base) // buf.element_size():][:g.numel()]
                          for g in bucket.gradients()]
                 self.optimizer.step_with_grads(list(params), views)
-            self.region_epoch[off] = self.grads.epoch
             self.buckets_fused += 1
             self.buckets_two_shot += 1
             fut2: torch.futures.Future = torch.futures.Future()
@@ -125,7 +148,6 @@ class FusedDDPState:
             self.grads.grad_out, self.grads.grad_out_sub = buf, off
         with torch.cuda.stream(self.side):
             self.optimizer.step_from_peers(list(params), self.grads)
-        self.region_epoch[off] = self.grads.epoch
         self.buckets_fused += 1
         fut: torch.futures.Future = torch.futures.Future()
         fut.set_result(buf)

@@ -80,24 +80,26 @@ def enable_gradient_release(
     """
     if grad_scaler is not None:
         raise NotImplementedError(
-            "GradScaler integration with enable_gradient_release is not yet implemented. "
-            "Per-parameter unscaling requires multiplying each grad by 1/scale, checking for "
-            "inf, and skipping steps on inf — this is planned but not yet available."
+            "gradient release cannot be combined with a GradScaler: the scaler decides whether to "
+            "skip a step only after it has seen every gradient, and by then the hooks have updated "
+            "the parameters. Pass grad_scaler=None (bf16 training needs no loss scaling)."
         )
     from torch.distributed.fsdp import FullyShardedDataParallel as FSDP1
     from torch.nn.parallel import DistributedDataParallel as DDP
 
     if isinstance(model, FSDP1):
         raise TypeError(
-            "enable_gradient_release() does not support FullyShardedDataParallel (FSDP1) "
-            "models. Use FSDP2 (fully_shard) instead, which is compatible with per-parameter "
-            "gradient release."
+            "the model is wrapped in FullyShardedDataParallel (FSDP1), whose flat parameters give "
+            "gradient hooks nothing to attach to; shard it with FSDP2 (torch.distributed.fsdp."
+            "fully_shard) to use gradient release."
         )
     if isinstance(model, DDP):
         # The reducer copies its bucket back into p.grad after the comm hook's future
         # resolves and no Python hook runs after that, so the gradient cannot be freed.
         raise TypeError(
-            "enable_gradient_release() does not support DistributedDataParallel (DDP). "
+            "the model is wrapped in DistributedDataParallel: its reducer writes the averaged bucket "
+            "back into p.grad after every Python hook has run, so a gradient cannot be consumed and "
+            "freed during backward. Use optimizer.step() with DDP, or fuse_ddp_allreduce()."
         )
 
     group_of = {id(p): g for g in optimizer.param_groups for p in g["params"]}

@@ -215,3 +215,131 @@ def test_the_model_notices_a_missing_wait():
             found = True
             break
     assert found
+
+
+# ---------------------------------------------------------------------------------------------
+# Fused DDP: buckets of one backward pass share one arena, and DDP rebuilds its buckets after
+# the first iteration, so the regions of consecutive passes overlap at different offsets.
+
+
+def _ddp_stream_program(dev, rank, world, queue, errors):
+    """One CUDA stream of one rank.  The hook copies buckets into the arena on the stream that
+    autograd runs on ("write" ops, preceded by the waits the layout asked for); the kernels run
+    on a side stream and each starts only after its own bucket was written (an event).
+    ``dev.buffers[owner]`` maps (offset, length) -> tag; ``dev.reading[reader]`` holds the
+    (owner, offset, length) a running kernel still reads."""
+    for op in queue:
+        kind = op[0]
+        if kind == "wait":
+            _, epoch = op
+            while any(dev.flag(rank, "done", s) < epoch for s in range(world)):
+                yield "blocked"
+        elif kind == "write":
+            _, off, n, tag, epoch = op
+            for reader, held in dev.reading.items():
+                for owner, o, m in held:
+                    if owner == rank and o < off + n and off < o + m:
+                        errors.append(f"rank {rank} overwrites [{off},{off + n}) while rank {reader} reads [{o},{o + m})")
+            mine = dev.buffers.setdefault(rank, {})
+            for (o, m) in [k for k in mine if k[0] < off + n and off < k[0] + k[1]]:
+                del mine[(o, m)]
+            mine[(off, n)] = tag
+            dev.pushed[("written", rank)] = epoch  # the event the side stream waits for
+        elif kind == "kernel":
+            _, epoch, off, n, tag = op
+            while dev.pushed.get(("written", rank), 0) < epoch:
+                yield "blocked"
+            for d in range(world):
+                dev.flags[d][("ready", rank)] = epoch
+            yield None
+            while any(dev.flag(rank, "ready", s) < epoch for s in range(world)):
+                yield "blocked"
+            dev.reading[("k", rank)] = {(s, off, n) for s in range(world)}
+            for s in range(world):
+                yield None
+                got = dev.buffers.get(s, {}).get((off, n))
+                if got != tag:
+                    errors.append(f"rank {rank} read {got} from rank {s} at {off}, expected {tag}")
+            dev.reading[("k", rank)] = set()
+            yield None
+            for d in range(world):
+                dev.flags[d][("done", rank)] = epoch
+        yield None
+
+
+def _ddp_host_queues(layouts, place):
+    """``layouts[step]`` = bucket sizes of that backward pass; ``place(index, nbytes, last_epoch)``
+    is the arena bookkeeping under test.  Returns the (autograd stream, side stream) queues."""
+    main, side, epoch = [], [], 0
+    for step, sizes in enumerate(layouts):
+        for index, n in enumerate(sizes):
+            off, wait_epoch = place(index, n, epoch)
+            if wait_epoch:
+                main.append(("wait", wait_epoch))
+            epoch += 1
+            main.append(("write", off, n, (step, index), epoch))
+            side.append(("kernel", epoch, off, n, (step, index)))
+    return main, side
+
+
+def _run_ddp_model(world, layouts, make_place, seeds):
+    for seed in seeds:
+        rng = random.Random(seed)
+        dev = _Device(world)
+        errors = []
+        programs = []
+        for r in range(world):
+            main, side = _ddp_host_queues(layouts, make_place())
+            programs.append(_ddp_stream_program(dev, r, world, main, errors))
+            programs.append(_ddp_stream_program(dev, r, world, side, errors))
+        alive, blocked = set(range(len(programs))), 0
+        while alive:
+            i = rng.choice(sorted(alive))
+            for _ in range(rng.choice([1, 1, 2, 5, 40])):
+                try:
+                    state = next(programs[i])
+                except StopIteration:
+                    alive.discard(i)
+                    break
+                if state == "blocked":
+                    blocked += 1
+                    break
+                blocked = 0
+            assert blocked < 400 * world, f"deadlock (seed {seed})"
+        if errors:
+            return errors
+    return []
+
+
+# First pass: buckets in the order of registration; afterwards DDP's rebuilt buckets (other
+# sizes, hence other offsets for everything but the first).
+_DDP_LAYOUTS = [[512, 1024, 256], [768, 1024], [512, 512, 1024], [256, 1536], [256, 1536]]
+
+
+@pytest.mark.parametrize("world", [2, 3, 4])
+def test_ddp_arena_survives_rebuilt_buckets(world):
+    from flashoptim_b200.parallel.ddp import ArenaLayout
+
+    errors = _run_ddp_model(world, _DDP_LAYOUTS, lambda: ArenaLayout(4096).place, range(40))
+    assert not errors, errors[:3]
+
+
+def test_the_ddp_model_notices_protection_keyed_by_offset():
+    """Control: waiting only for the last use of the SAME offset (what an exact-offset map does)
+    lets a rebuilt bucket overwrite a region that a slower peer still reads."""
+
+    def make_place():
+        cursor, last_use = [0], {}
+
+        def place(index, nbytes, last_epoch):
+            if index == 0:
+                cursor[0] = 0
+            off = cursor[0]
+            cursor[0] += (nbytes + 255) // 256 * 256
+            wait_epoch = last_use.get(off, 0)
+            last_use[off] = last_epoch + 1  # the epoch this bucket's kernel will get
+            return off, wait_epoch
+
+        return place
+
+    assert _run_ddp_model(2, _DDP_LAYOUTS, make_place, range(200))

@@ -154,8 +154,116 @@ def _dcp_worker(rank, world, use_cuda, ckpt_root):
     return errors
 
 
+def _accum_worker(rank, world, use_cuda):
+    """Gradient accumulation with ``set_requires_gradient_sync``: two micro-batches per step,
+    only the second one reduce-scatters; compared every step with a single process that sees
+    both micro-batches of every rank (the reference's "grad_accum" setting,
+    test/test_fsdp2.py:95-115, 444-455)."""
+    from torch.distributed.fsdp import fully_shard
+
+    device = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
+    errors = []
+    g = torch.Generator().manual_seed(11)
+    data = [(torch.randn(world * 8, 10, generator=g), torch.randint(0, 6, (world * 8,), generator=g))
+            for _ in range(8)]
+    for cls, kw in ((FlashAdamW, dict(lr=5e-4, weight_decay=1e-2)), (FlashLion, dict(lr=5e-4))):
+        for dtype, mwb, quantize in CONFIGS:
+            tag = f"accumulation {cls.__name__} {dtype} mwb={mwb}"
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                single, sharded = _net(dtype, device), _net(dtype, device)
+                for layer in sharded:
+                    if isinstance(layer, nn.Linear):
+                        fully_shard(layer)
+                fully_shard(sharded)
+                o1 = cls(single.parameters(), master_weight_bits=mwb, quantize=quantize, **kw)
+                o2 = cls(sharded.parameters(), master_weight_bits=mwb, quantize=quantize, **kw)
+            tol = get_tolerances(dtype, quantize)
+            for step in range(4):
+                for micro in range(2):
+                    x, y = data[2 * step + micro]
+                    x, y = x.to(device=device, dtype=dtype), y.to(device)
+                    xs, ys = x[rank * 8:(rank + 1) * 8], y[rank * 8:(rank + 1) * 8]
+                    (nn.functional.cross_entropy(single(x).float(), y) / 2).backward()
+                    sharded.set_requires_gradient_sync(micro == 1)
+                    (nn.functional.cross_entropy(sharded(xs).float(), ys) / 2).backward()
+                o1.step(); o1.zero_grad()
+                o2.step(); o2.zero_grad()
+                for (n1, p1), (_, p2) in zip(single.named_parameters(), sharded.named_parameters()):
+                    errors += check_similar(_full(p2.detach()), p1.detach(), tol, f"{tag} step {step} {n1}")
+    return errors
+
+
+def _fp32_roundtrip_worker(rank, world, use_cuda):
+    """``get_fp32_model_state_dict`` -> ``set_fp32_model_state_dict`` under sharding restores
+    weights and correction codes exactly, also after the model was disturbed in between, and a
+    second export equals the first (the reference's test/test_fsdp2.py:646-705)."""
+    from torch.distributed.fsdp import fully_shard
+
+    device = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
+    errors = []
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(world * 8, 10, generator=g)
+    y = torch.randint(0, 6, (world * 8,), generator=g)
+    for mwb in (24, 32):
+        tag = f"fp32 round trip mwb={mwb}"
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            model = _net(torch.bfloat16, device)
+            for layer in model:
+                if isinstance(layer, nn.Linear):
+                    fully_shard(layer)
+            fully_shard(model)
+            opt = FlashAdamW(model.parameters(), lr=1e-3, master_weight_bits=mwb)
+        xs = x[rank * 8:(rank + 1) * 8].to(device=device, dtype=torch.bfloat16)
+        ys = y[rank * 8:(rank + 1) * 8].to(device)
+        for _ in range(3):
+            nn.functional.cross_entropy(model(xs).float(), ys).backward()
+            opt.step(); opt.zero_grad()
+        first = {k: v.clone() for k, v in opt.get_fp32_model_state_dict(model).items()}
+        weights = {n: p.to_local().detach().clone() for n, p in model.named_parameters()}
+        codes = {n: opt.state[p]["error_bits"].clone() for n, p in model.named_parameters()}
+        for n, p in model.named_parameters():
+            if first[n].dtype != torch.float32 or first[n].shape != p.to_local().shape:
+                errors.append(f"{tag}: export of {n} is {first[n].dtype} {tuple(first[n].shape)}")
+        with torch.no_grad():  # disturb weights and codes, then import the export
+            for p in model.parameters():
+                p.to_local().mul_(1.5)
+                opt.state[p]["error_bits"].zero_()
+        opt.set_fp32_model_state_dict(model, first)
+        for n, p in model.named_parameters():
+            if not torch.equal(p.to_local().detach(), weights[n]):
+                errors.append(f"{tag}: weights of {n} differ after the import")
+            if not torch.equal(opt.state[p]["error_bits"], codes[n]):
+                errors.append(f"{tag}: correction codes of {n} differ after the import")
+        second = opt.get_fp32_model_state_dict(model)
+        for k, v in first.items():
+            if not torch.equal(second[k], v):
+                errors.append(f"{tag}: second export of {k} differs from the first")
+        nn.functional.cross_entropy(model(xs).float(), ys).backward()
+        opt.step(); opt.zero_grad()
+        if not all(torch.isfinite(_full(p.detach()).float()).all() for p in model.parameters()):
+            errors.append(f"{tag}: non-finite weights after continuing")
+    return errors
+
+
 def test_fsdp2_gloo_two_ranks():
     run_distributed(_train_worker, world_size=2, backend="gloo", args=(False,))
+
+
+def test_fsdp2_gradient_accumulation_gloo():
+    run_distributed(_accum_worker, world_size=2, backend="gloo", args=(False,))
+
+
+def test_fsdp2_fp32_state_dict_round_trip_gloo():
+    run_distributed(_fp32_roundtrip_worker, world_size=2, backend="gloo", args=(False,))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_fsdp2_accumulation_and_fp32_round_trip_nccl_two_gpus():
+    run_distributed(_accum_worker, world_size=2, backend="nccl", args=(True,))
+    run_distributed(_fp32_roundtrip_worker, world_size=2, backend="nccl", args=(True,))
 
 
 def test_fsdp2_dcp_gloo_two_ranks():

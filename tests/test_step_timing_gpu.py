@@ -1,0 +1,115 @@
+"""Timing guards for the fused step kernels (CUDA events, after warm-up).
+
+The reference's only performance test (``test/test_optimizers.py:639-708``) asserts, with
+wall-clock time, that its fused step (with and without master-weight correction) is no slower
+than the eager formulation with quantised states and than the eager formulation without, plus
+0.2 ms of slack, for square tensors from 32^2 to 16384^2.  The same inequalities are checked here
+with device timing, and two more that guard this library's own claims: a multi-tensor launch over
+a few hundred tensors costs about what one tensor of the same size costs, and the staged
+(bulk-copy) kernels are not slower than the register-path kernels they replace by default.
+These tests catch a silent fall-back to the eager path or to the register path; they do not
+pin absolute speeds (those are in the benchmark scripts).
+"""
+
+import pytest
+import torch
+
+import flashoptim_b200 as fo
+
+pytestmark = pytest.mark.gpu
+
+SLACK_MS = 0.2
+
+
+def _ms_per_step(opt, iters):
+    for _ in range(3):
+        opt.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        opt.step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+@pytest.mark.parametrize("opt_name", ["adamw", "lion", "sgdw"])
+@pytest.mark.parametrize("d", [32, 256, 1024, 4096, 16384])
+def test_fused_step_is_as_fast_as_the_eager_formulations(opt_name, d):
+    import warnings
+
+    warnings.simplefilter("ignore")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    w = torch.randn(d, d, device="cuda", generator=g).clip_(-1.75, 1.75).to(torch.bfloat16).requires_grad_(True)
+    w.grad = torch.randn(d, d, device="cuda", generator=g).to(torch.bfloat16)
+    iters = max(3, min(100, -(-1_000_000 // w.numel())))
+
+    def make(**kw):
+        common = dict(lr=1e-3, weight_decay=0.01, check_numerics=False)
+        if opt_name == "adamw":
+            return fo.FlashAdamW([w], **common, **kw)
+        if opt_name == "lion":
+            return fo.FlashLion([w], **common, **kw)
+        return fo.FlashSGDW([w], momentum=0.9, **common, **kw)
+
+    times = {}
+    for key in [(False, False, None), (True, False, None), (True, True, None), (True, True, 24), (True, True, 32)]:
+        quantize, fused, mwb = key
+        times[key] = _ms_per_step(make(quantize=quantize, fused=fused, master_weight_bits=mwb), iters)
+    t_noquant, t_nofuse = times[(False, False, None)], times[(True, False, None)]
+    for key in [(True, True, None), (True, True, 24), (True, True, 32)]:
+        assert times[key] < t_nofuse + SLACK_MS, (key, times)
+        assert times[key] < t_noquant + SLACK_MS, (key, times)
+
+
+def test_multi_tensor_launch_costs_what_one_tensor_costs():
+    """291 tensors with the sizes of a (width-reduced) Llama layer list, one fused launch, against
+    ONE tensor holding the same number of elements: within 10 % (+0.05 ms), because the grid walks
+    chunks, not tensors.  The reference launches once per tensor instead."""
+    import warnings
+
+    warnings.simplefilter("ignore")
+    d, ffn, vocab = 1024, 3584, 32064
+    shapes = [(vocab, d)]
+    for _ in range(32):
+        shapes += [(d, d), (d // 4, d), (d // 4, d), (d, d), (ffn, d), (ffn, d), (d, ffn), (d,), (d,)]
+    shapes += [(d,), (vocab, d)]
+    assert len(shapes) == 291
+    g = torch.Generator(device="cuda").manual_seed(0)
+    many = []
+    for s in shapes:
+        p = torch.nn.Parameter((torch.randn(s, device="cuda", generator=g) * 0.02).to(torch.bfloat16))
+        p.grad = (torch.randn(s, device="cuda", generator=g) * 1e-3).to(torch.bfloat16)
+        many.append(p)
+    n = sum(p.numel() for p in many)
+    one = torch.nn.Parameter((torch.randn(n, device="cuda", generator=g) * 0.02).to(torch.bfloat16))
+    one.grad = (torch.randn(n, device="cuda", generator=g) * 1e-3).to(torch.bfloat16)
+    from flashoptim_b200.ops import step as fo_step
+
+    opt_many = fo.FlashAdamW(many, lr=1e-4, master_weight_bits=24)
+    opt_one = fo.FlashAdamW([one], lr=1e-4, master_weight_bits=24)
+    n0 = fo_step.launch_count()
+    t_many = _ms_per_step(opt_many, 10)
+    assert fo_step.launch_count() - n0 == 13, "one fused launch per step expected"
+    t_one = _ms_per_step(opt_one, 10)
+    assert t_many <= 1.1 * t_one + 0.05, (t_many, t_one)
+
+
+def test_staged_kernels_are_not_slower_than_the_register_path():
+    import warnings
+
+    warnings.simplefilter("ignore")
+    from flashoptim_b200.ops.step import set_step_variant
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    w = torch.nn.Parameter((torch.randn(16384, 16384, device="cuda", generator=g) * 0.02).to(torch.bfloat16))
+    w.grad = (torch.randn(16384, 16384, device="cuda", generator=g) * 1e-3).to(torch.bfloat16)
+    try:
+        times = {}
+        for variant in (0, 1):
+            set_step_variant(variant)
+            times[variant] = _ms_per_step(fo.FlashAdamW([w], lr=1e-4, master_weight_bits=24), 10)
+    finally:
+        set_step_variant(1)
+    assert times[1] <= times[0] * 1.03 + 0.02, times
