@@ -54,12 +54,14 @@ def parse_args():
                     help="ours only: fuse the FSDP2 collectives with the update where supported")
     ap.add_argument("--comm-ctas", type=int, default=-1,
                     help="grid cap of the fused reduce-scatter kernel (0: fill the GPU; -1: the measured default, "
-                         "see DEFAULT_COMM_CTAS)")
+                         "flashoptim_b200.parallel.tuned_options)")
     ap.add_argument("--sweep", default=None,
                     help="ours, >= 2 GPUs: instead of the benchmark line, time every listed configuration in this "
                          "one process and print them as one JSON line.  Semicolon-separated entries "
                          "MODE[:CTAS[:LOADS]] with MODE nccl (FSDP2's NCCL collectives + this library's step), "
-                         "fused (reduce-scatter fused with the update) or push (fused + all-gather on write), "
+                         "fused (reduce-scatter fused with the update, NCCL all-gather), push (fused + all-gather "
+                         "on write), pull / pullce (fused + this library's all-gather by pull kernel / by copy "
+                         "engines) or agce (NCCL reduce-scatter, copy-engine all-gather), "
                          "CTAS the grid cap (0: none) and LOADS mc (multimem.ld_reduce), p2p (peer loads into "
                          "registers) or staged (bulk copies of the peers' chunks into shared memory); p2pmc / stagedmc "
                          "push the parameters with multimem.st instead of one store per rank; ce / cestaged move all "
@@ -68,18 +70,22 @@ def parse_args():
     ap.add_argument("--transport", default="auto", choices=["auto", "kernel", "copy_engine"],
                     help="fused path: the update kernel itself reads the peers' gradients over NVLink (kernel) "
                          "or copy engines bring them into local memory first (copy_engine); auto: the measured "
-                         "default, see DEFAULT_COMM_TRANSPORT")
+                         "default: kernel")
     ap.add_argument("--push-multicast", default="auto", choices=["auto", "on", "off"],
                     help="parameter push through multimem.st (auto: as the gradient loads; with staged kernels "
                          "above 2 GPUs)")
     ap.add_argument("--comm-kernel", default="auto", choices=["auto", "register", "staged"],
                     help="fused path: register-path or bulk-copy staged reduce-scatter + update kernels "
-                         "(auto: the measured default, see DEFAULT_COMM_KERNEL)")
+                         "(auto: the measured default, flashoptim_b200.parallel.tuned_options)")
     ap.add_argument("--timeline", default=None,
                     help="write a summary of a torch.profiler trace of two steps (kernel time per stream and "
                          "per kernel family, rank 0) to this file; never a benchmark number")
     ap.add_argument("--own-all-gather", action="store_true",
                     help="fused path: FSDP2's parameter all-gather through this library's pull kernel")
+    ap.add_argument("--all-gather", default="auto", choices=["auto", "copy_engine", "nccl"],
+                    help="fused path: copy_engine = FSDP2's parameter all-gather as cudaMemcpyAsync pulls between "
+                         "two flag kernels (no SM, three group-sized buffers); auto: all-gather on write where "
+                         "--push-params allows, else NCCL")
     ap.add_argument("--push-params", default="auto", choices=["auto", "on", "off"],
                     help="fused path: the update kernel also stores the new parameters into every rank's "
                          "all-gather buffer, so FSDP2's parameter all-gathers move no data; auto = on at "
@@ -102,34 +108,8 @@ def load_module_from(path: str, name: str):
     return mod
 
 
-# Defaults of the fused FSDP2 path by world size, taken from sweeps on 8 x B200
-# (`--sweep`, tables in DESIGN.md): grid cap of the reduce-scatter + update kernel (0: none).
-DEFAULT_COMM_CTAS = {2: 0, 4: 0, 8: 0}
-# All-gather on write keeps one unsharded copy of the parameters per GPU; "auto" turns it on
-# while that copy stays below this many GiB.
-PUSH_AUTO_MAX_GIB = 24.0
-
-
-def default_comm_ctas(world: int, multicast: bool) -> int:
-    del multicast
-    return DEFAULT_COMM_CTAS.get(world, 0)
-
-
-# Bulk-copy staged reduce-scatter + update kernels by world size (same sweeps).
-DEFAULT_COMM_KERNEL = {2: "register", 4: "register", 8: "register"}
-
-
-# Who moves the gradient bytes: the update kernel (peer loads / multimem / bulk copies) or the
-# copy engines (cudaMemcpyAsync into a local staging buffer, then a local update kernel).
-DEFAULT_COMM_TRANSPORT = {2: "kernel", 4: "kernel", 8: "kernel"}
-
-
-def default_comm_staged(world: int) -> bool:
-    return DEFAULT_COMM_KERNEL.get(world, "register") == "staged"
-
-
-def push_default(world: int, n_params: int) -> bool:
-    return world >= 2 and n_params * 2 / 2**30 <= PUSH_AUTO_MAX_GIB
+# Defaults of the fused FSDP2 path: flashoptim_b200.parallel.tuned_options(world, bytes), i.e.
+# what the sweeps of this script (`--sweep`) measured best on 2, 4 and 8 B200s.
 
 
 def measured_hbm_gbs() -> float:
@@ -336,28 +316,33 @@ def main():
     fused_state = None
     if args.sweep and (args.impl != "ours" or world < 2):
         raise SystemExit("--sweep compares this library's collective paths: it needs --impl ours and >= 2 GPUs")
-    use_multicast = (world > 2) if args.multicast == "auto" else args.multicast == "on"
-    if args.no_multicast:
-        use_multicast = False
-    push_params = push_default(world, n_params) if args.push_params == "auto" else args.push_params == "on"
-    if args.own_all_gather:
+    tuned = {}
+    if args.impl == "ours" and world > 1:
+        from flashoptim_b200.parallel import tuned_options
+
+        tuned = tuned_options(world, n_params * 2)  # bf16 parameters
+    staged = tuned.get("staged", False) if args.comm_kernel == "auto" else args.comm_kernel == "staged"
+    transport = "kernel" if args.transport == "auto" else args.transport
+    use_multicast = tuned.get("use_multicast", False) if args.multicast == "auto" else args.multicast == "on"
+    if args.no_multicast or ((staged or transport == "copy_engine") and args.multicast != "on"):
+        use_multicast = False  # staged kernels and copy engines read the peers' buffers directly
+    comm_ctas = tuned.get("max_ctas", 0) if args.comm_ctas < 0 else args.comm_ctas
+    push_mc = tuned.get("push_multicast", use_multicast) if args.push_multicast == "auto" else args.push_multicast == "on"
+    push_params = tuned.get("push_params", False) if args.push_params == "auto" else args.push_params == "on"
+    ag_ce = (tuned.get("all_gather_copy_engine", False) and not push_params) if args.all_gather == "auto" \
+        else args.all_gather == "copy_engine"
+    own_ag = args.own_all_gather or ag_ce
+    if own_ag and args.push_params != "on":
         push_params = False
-    comm_ctas = default_comm_ctas(world, use_multicast) if args.comm_ctas < 0 else args.comm_ctas
-    staged = default_comm_staged(world) if args.comm_kernel == "auto" else args.comm_kernel == "staged"
-    if staged and args.multicast != "on":
-        use_multicast = False  # the staged kernels read the peers' buffers with bulk copies
-    transport = DEFAULT_COMM_TRANSPORT.get(world, "kernel") if args.transport == "auto" else args.transport
-    if transport == "copy_engine" and args.multicast != "on":
-        use_multicast = False
-    push_mc = (use_multicast or (staged and world > 2)) if args.push_multicast == "auto" else args.push_multicast == "on"
     if args.sweep:  # every variant must be reachable by flipping switches at run time
-        use_multicast, push_params = True, True
+        use_multicast, push_params, own_ag = True, True, True
     if args.impl == "ours" and args.fused_comm == "auto":
         try:
             from flashoptim_b200.parallel import fsdp as fo_fsdp
 
             fused_state = fo_fsdp.enable_fused_fsdp(model, opt, timeout_s=20.0, max_ctas=comm_ctas,
-                                                    use_multicast=use_multicast, own_all_gather=args.own_all_gather,
+                                                    use_multicast=use_multicast, own_all_gather=own_ag,
+                                                    all_gather_copy_engine=ag_ce,
                                                     push_params=push_params, staged=staged, push_multicast=push_mc,
                                                     transport=transport,
                                                     push_budget_bytes=int(args.push_budget_gb * 2**30) or None)
@@ -447,11 +432,13 @@ def main():
             ctas = int(f[1]) if len(f) > 1 and f[1] else 0
             loads = f[2] if len(f) > 2 and f[2] else "mc"
             cap_all = len(f) > 3 and f[3] == "capall"
-            if mode not in ("nccl", "fused", "push") or loads not in ("mc", "p2p", "p2pmc", "staged", "stagedmc",
+            if mode not in ("nccl", "fused", "push", "pull", "pullce", "agce") or loads not in ("mc", "p2p", "p2pmc", "staged", "stagedmc",
                                                                       "ce", "cestaged"):
                 raise SystemExit(f"--sweep: bad entry {entry!r}")
-            fused_state.enabled = mode != "nccl"
-            fused_state.push_enabled = mode == "push"
+            fused_state.enabled = mode not in ("nccl", "agce")
+            fused_state.ag_copy_engine = mode in ("pullce", "agce")
+            fused_state.set_all_gather_mode({"push": "push", "pull": "pull", "pullce": "pull", "agce": "pull"}
+                                            .get(mode, "nccl"))
             fused_state.peers.max_ctas = ctas
             fused_state.peers.use_multicast = loads == "mc"
             fused_state.peers.variant = 1 if "staged" in loads else 0
@@ -464,6 +451,7 @@ def main():
             fused_state.check()
             c0 = (fused_state.fused_calls, fused_state.fallbacks, fused_state.ag_eliminated, fused_state.ag_fallbacks)
             torch.cuda.reset_peak_memory_stats()
+            ag0 = fused_state.ag_calls
             ms = timed_steps(args.steps)
             fused_state.check()
             c1 = (fused_state.fused_calls, fused_state.fallbacks, fused_state.ag_eliminated, fused_state.ag_fallbacks)
@@ -471,10 +459,11 @@ def main():
                 "entry": entry.strip(), "mode": mode, "comm_ctas": ctas, "loads": loads if mode != "nccl" else None,
                 "last_group_full_grid": not cap_all,
                 "ms_per_step": round(ms, 3), "tokens_per_s": round(world * b * s / (ms * 1e-3), 1),
-                "peak_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2),
+                "peak_gib": round((torch.cuda.max_memory_allocated() + fused_state.peers.symmetric_bytes) / 2**30, 2),
                 "per_step": {k: (y - x) / args.steps for k, x, y in
                              zip(("fused_rs", "nccl_rs", "ag_eliminated", "nccl_ag"), c0, c1)},
             })
+            results[-1]["per_step"]["own_ag"] = (fused_state.ag_calls - ag0) / args.steps
             if rank == 0:
                 print(f"[sweep] {results[-1]}", file=sys.stderr, flush=True)
         sampler.stop()
@@ -509,7 +498,11 @@ def main():
     if fused_state is not None:
         fused_state.check()
     dist.barrier()
-    peak_bytes = torch.cuda.max_memory_allocated()
+    # symmetric (NVLink-mapped) buffers are not seen by PyTorch's allocator statistics
+    symmetric_bytes = fused_state.peers.symmetric_bytes if fused_state is not None else 0
+    peak_bytes = torch.cuda.max_memory_allocated() + symmetric_bytes
+    free_b, total_b = torch.cuda.mem_get_info()
+    device_used = total_b - free_b  # the driver's view: context, NCCL, allocator reserve, symmetric memory
 
     # ---- the optimizer step alone (the second half of the headline metric): gradients of one
     # more backward pass are kept and optimizer.step() is timed on them, on this rank's shards
@@ -582,9 +575,9 @@ def main():
         dcp_times = {"save_s": round(t1 - t0, 3), "load_s": round(t2 - t1, 3), "bytes_on_disk": size,
                      "compressed": bool(args.compress_state_dict)}
 
-    t = torch.tensor([e2e_ms, peak_bytes / 2**30], device=dev, dtype=torch.float64)
+    t = torch.tensor([e2e_ms, peak_bytes / 2**30, device_used / 2**30], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms, peak_gib = (float(x) for x in t.tolist())
+    e2e_ms, peak_gib, used_gib = (float(x) for x in t.tolist())
     tokens_per_step = world * b * s
     if rank == 0:
         rec = {
@@ -611,6 +604,8 @@ def main():
                 "fused_comm_ctas": comm_ctas if fused_comm else None,
                 "fused_comm_kernel": ("staged" if staged else "register") if fused_comm else None,
                 "fused_comm_transport": transport if fused_comm else None,
+                "fused_all_gather": (fused_state.all_gather_mode + ("/copy_engine" if fused_state.ag_copy_engine and
+                                     fused_state.all_gather_mode == "pull" else "")) if fused_comm else None,
                 **({"fused_comm_error": fused_error} if fused_error else {}),
                 "activation_checkpointing": bool(cfg.activation_checkpointing),
                 "l2": "working set (>= 16 GB of weights) far exceeds the 126 MB L2; no flush",
@@ -625,6 +620,9 @@ def main():
             },
             "gpu_launches": n_launch,
             "peak_gib_per_gpu": round(peak_gib, 2),
+            "peak_gib_note": "torch.cuda.max_memory_allocated plus this library's symmetric NVLink buffers "
+                             f"({symmetric_bytes / 2**30:.2f} GiB, invisible to the allocator statistics)",
+            "device_used_gib_per_gpu": round(used_gib, 2),
             "clocks": sampler.summary(),
         }
         if step_stats is not None:

@@ -81,9 +81,13 @@ def main() -> None:
                      compress_state_dict=args.compress_state_dict)
     fused = None
     if args.fused and args.device == "cuda":
-        from flashoptim_b200.parallel import enable_fused_fsdp
+        from flashoptim_b200.parallel import enable_fused_fsdp, tuned_options
 
-        fused = enable_fused_fsdp(model, opt, push_params=args.push_params)
+        # kernel, grid cap and load path that measured best for this number of GPUs; the
+        # all-gather on write costs an unsharded copy of the parameters and is opt-in here
+        opts = tuned_options(world)
+        opts.pop("own_all_gather", None), opts.pop("all_gather_copy_engine", None)
+        fused = enable_fused_fsdp(model, opt, push_params=args.push_params, **opts)
     if args.gradient_release:
         enable_gradient_release(model, opt)
 

@@ -200,9 +200,11 @@ class PeerAllGather(AllGather):  # type: ignore[misc,valid-type]
     FSDP2 allocates the ``[world, shard]`` all-gather output through :meth:`allocate`
     (here: a symmetric buffer from a small pool), copies its own shards into slot
     ``rank`` and calls the communicator; every rank then pulls slot ``s`` from rank
-    ``s`` over NVLink with plain 16-byte peer loads (``fo_allgather_peer``).  Calls whose
-    slot size is not a multiple of 16 bytes, or that are larger than the pool's buffers,
-    use NCCL.
+    ``s`` over NVLink with plain 16-byte peer loads (``fo_allgather_peer``) or, with
+    ``ctx.ag_copy_engine``, with one ``cudaMemcpyAsync`` per peer between two one-CTA flag
+    kernels: the copy engines then move the bytes and no SM is taken from the GEMMs that the
+    all-gather overlaps.  Calls whose slot size is not a multiple of 16 bytes, or that are
+    larger than the pool's buffers, use NCCL.
     """
 
     def __init__(self, ctx: "FusedFSDPState") -> None:
@@ -227,10 +229,20 @@ class PeerAllGather(AllGather):  # type: ignore[misc,valid-type]
             self.ctx.ag_fallbacks += 1
             return dist.all_gather_into_tensor(output_tensor, input_tensor, group=group, async_op=async_op)
         slot_bytes = input_tensor.numel() * input_tensor.element_size()
-        args = slot.next_args()
-        rc = native.load().fo_allgather_peer(slot_bytes, ctypes.byref(args),
-                                             native.stream_ptr(self.ctx.peers.device))
-        native.check(rc, "fo_allgather_peer")
+        peers = self.ctx.peers
+        if self.ctx.ag_copy_engine:
+            w, r = peers.world, peers.rank
+            slot.epoch += 1
+            args = peers.comm_args(slot.buf, slot.epoch, slot.ready_channel, slot.done_channel)
+            peers.barrier(args)  # every rank's shards are in its own slot
+            for i in range(1, w):
+                s = (r + i) % w  # every rank starts with a different peer
+                peers.copy(slot.buf.ptrs[r] + s * slot_bytes, slot.buf.ptrs[s] + s * slot_bytes, slot_bytes)
+            peers.signal(args, slot.done_channel)  # my reads of the peers' slots are complete
+        else:
+            args = slot.next_args()
+            rc = native.load().fo_allgather_peer(slot_bytes, ctypes.byref(args), native.stream_ptr(peers.device))
+            native.check(rc, "fo_allgather_peer")
         self.ctx.ag_calls += 1
         return None
 
@@ -345,8 +357,10 @@ def _fsdp_param_groups(model: nn.Module) -> list:
 class FusedFSDPState:
     def __init__(self, model: nn.Module, optimizer: FlashOptimizer, group, timeout_s, use_multicast, depth,
                  max_ctas=0, own_all_gather=False, push_params=False, push_budget_bytes=None,
-                 last_group_full_grid=True, staged=False, push_multicast=None, transport="kernel"):
+                 last_group_full_grid=True, staged=False, push_multicast=None, transport="kernel",
+                 all_gather_copy_engine=False):
         self.optimizer = optimizer
+        self.ag_copy_engine = bool(all_gather_copy_engine)  # own_all_gather: copy engines, not the pull kernel
         if transport not in ("kernel", "copy_engine"):
             raise ValueError(f"transport must be 'kernel' or 'copy_engine', got {transport!r}")
         self.transport = transport  # may be switched between steps (for comparisons)
@@ -383,11 +397,11 @@ class FusedFSDPState:
         self.ag_fallbacks = 0
         self.ag_eliminated = 0
         self.gathers: list[PushedAllGather] = []
-        if push_params and own_all_gather:
-            raise ValueError("push_params and own_all_gather are alternatives")
         # every symmetric allocation comes first and the communicators are installed last, so
         # that a failed allocation leaves the model on FSDP2's own collectives
-        installs: list[tuple[nn.Module, object]] = []
+        self._push_installs: list[tuple[nn.Module, object]] = []
+        self._pull_installs: list[tuple[nn.Module, object]] = []
+        self._listener = None
         if push_params:
             by_param = {}
             chosen = select_push_groups(
@@ -399,7 +413,7 @@ class FusedFSDPState:
                 gather = PushedAllGather(self, comm)
                 comm.gather = gather
                 self.gathers.append(gather)
-                installs.append((m, gather))
+                self._push_installs.append((m, gather))
                 for fp in comm.fsdp_params:
                     by_param[id(fp.sharded_param)] = gather
 
@@ -410,18 +424,46 @@ class FusedFSDPState:
                         g.invalidate()
 
             optimizer._local_update_listeners.append(on_local_update)
+            self._listener = on_local_update
         if own_all_gather:
             # the all-gather output of a group is as large as its reduce-scatter input;
             # three buffers: one being copied out, one prefetched, one spare
             self.ag_pool_bytes = need
             self.ag_pool = _Pool(self.peers, need, 3)
-            installs += [(m, PeerAllGather(self)) for m, _ in groups]
+            self._pull_installs = [(m, PeerAllGather(self)) for m, _ in groups]
         for m, comm in self.comms:
             m.set_custom_reduce_scatter(comm)
-        for m, gather in installs:
-            m.set_custom_all_gather(gather)
+        self._installs: list[tuple[nn.Module, object]] = []
+        self.all_gather_mode = "nccl"
+        self.set_all_gather_mode("push" if push_params else ("pull" if own_all_gather else "nccl"))
+
+    def set_all_gather_mode(self, mode: str) -> None:
+        """Which parameter all-gather FSDP2 uses from now on (collective: every rank, between
+        steps): ``"push"`` (all-gather on write; groups without a push buffer use this library's
+        all-gather where that was set up, else NCCL),
+        ``"pull"`` (this library's all-gather: pull kernel or copy engines) or ``"nccl"``.
+        Only modes whose buffers were allocated at construction are available."""
+        from torch.distributed.fsdp._fully_shard._fsdp_collectives import DefaultAllGather
+
+        if mode not in ("push", "pull", "nccl"):
+            raise ValueError(f"unknown all-gather mode {mode!r}")
+        if (mode == "push" and not self._push_installs) or (mode == "pull" and not self._pull_installs):
+            raise ValueError(f"all-gather mode {mode!r} was not set up when the fused path was enabled")
+        for m, _ in self._installs:
+            m.set_custom_all_gather(DefaultAllGather())
+        installs = {"push": list(self._push_installs), "pull": list(self._pull_installs), "nccl": []}[mode]
+        if mode == "push":
+            # groups that got no push buffer (memory budget): this library's all-gather if it was
+            # set up, else FSDP2's
+            pushed = {id(m) for m, _ in installs}
+            installs += [(m, g) for m, g in self._pull_installs if id(m) not in pushed]
         self._installs = installs
-        self._listener = on_local_update if push_params else None
+        for m, gather in self._installs:
+            m.set_custom_all_gather(gather)
+        for g in self.gathers:
+            g.invalidate()  # whatever the buffers hold now was not necessarily put there by a push
+        self.push_enabled = mode == "push"
+        self.all_gather_mode = mode
 
     @property
     def staging(self) -> torch.Tensor:
@@ -455,6 +497,37 @@ class FusedFSDPState:
         self.peers.poll_status()
 
 
+# All-gather on write keeps one unsharded copy of the parameters on every GPU; tuned_options()
+# proposes it while that copy stays below this many bytes.
+PUSH_AUTO_MAX_BYTES = 24 * 2**30
+
+
+def tuned_options(world_size: int, unsharded_param_bytes: int = 0) -> dict:
+    """Keyword arguments for :func:`enable_fused_fsdp` that measured best for Llama-3-8B training
+    steps on 2, 4 and 8 B200s of one NVSwitch node (``bench.py --sweep``; the tables are in the
+    repository's design notes).
+
+    * Two ranks: the kernel is bound by its own arithmetic and HBM, not by the link; the
+      bulk-copy staged kernel on the whole GPU finishes soonest, parameters are pushed with one
+      store per rank.
+    * More ranks: NVLink-bound.  ``multimem.ld_reduce`` lets the switch add the ranks' copies,
+      four units per thread are in flight, and 48 CTAs keep the links busy while the other SMs
+      stay with backward's GEMMs; parameters are pushed with ``multimem.st``.
+    * ``push_params`` (all-gather on write) is proposed when ``unsharded_param_bytes`` is given
+      and at most :data:`PUSH_AUTO_MAX_BYTES`; otherwise FSDP2's parameter all-gather is done by
+      the copy engines (``own_all_gather`` + ``all_gather_copy_engine``), which costs three
+      group-sized buffers."""
+    if world_size <= 2:
+        opts = dict(use_multicast=False, staged=True, max_ctas=0, push_multicast=False)
+    else:
+        opts = dict(use_multicast=True, staged=False, max_ctas=48, push_multicast=True)
+    if 0 < unsharded_param_bytes <= PUSH_AUTO_MAX_BYTES:
+        opts["push_params"] = True
+    else:
+        opts.update(own_all_gather=True, all_gather_copy_engine=True)
+    return opts
+
+
 def enable_fused_fsdp(
     model: nn.Module,
     optimizer: FlashOptimizer,
@@ -471,6 +544,7 @@ def enable_fused_fsdp(
     staged: bool = False,
     push_multicast: Optional[bool] = None,
     transport: str = "kernel",
+    all_gather_copy_engine: bool = False,
 ) -> Optional[FusedFSDPState]:
     """Fuse FSDP2's gradient reduce-scatter with ``optimizer``'s sharded update.
 
@@ -503,8 +577,10 @@ def enable_fused_fsdp(
     parameters go to the peers' all-gather buffers in further copy-engine copies.  It costs one
     more pass of the gradients through HBM and one local ``[world, shard]`` staging buffer, and
     leaves every SM to backward's GEMMs while the links are busy.
-    ``own_all_gather`` also replaces FSDP2's parameter all-gather by this library's
-    pull kernel over symmetric buffers (:class:`PeerAllGather`).
+    ``own_all_gather`` also replaces FSDP2's parameter all-gather by this library's own over
+    symmetric buffers (:class:`PeerAllGather`): a pull kernel, or with ``all_gather_copy_engine``
+    one ``cudaMemcpyAsync`` per peer, which takes no SM from the GEMMs it overlaps and costs
+    three group-sized buffers instead of an unsharded copy of the model.
     ``push_params`` instead removes that all-gather: the update kernel stores the new
     parameters into every rank's all-gather buffer (:class:`PushedAllGather`); costs one
     unsharded copy of the parameters per rank (``.ag_eliminated`` counts the all-gathers
@@ -517,7 +593,8 @@ def enable_fused_fsdp(
     state, error = None, None
     try:
         state = FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas, own_all_gather,
-                               push_params, push_budget_bytes, last_group_full_grid, staged, push_multicast, transport)
+                               push_params, push_budget_bytes, last_group_full_grid, staged, push_multicast, transport,
+                               all_gather_copy_engine)
     except UnsupportedFSDPInternals as e:
         # same PyTorch on every rank, so every rank lands here together, before any collective
         import warnings

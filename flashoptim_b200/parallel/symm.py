@@ -89,6 +89,9 @@ class PeerGroup:
         # 1: bulk-copy staged step kernels where they apply (peer loads, 8-bit states, bf16/fp16)
         self.variant = variant
         self.max_ctas = max_ctas  # grid cap of the peer kernels (0: fill the GPU)
+        # bytes of symmetric memory handed out so far; PyTorch's caching-allocator statistics
+        # (torch.cuda.max_memory_allocated) do not see these allocations
+        self.symmetric_bytes = 0
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._pad = self.allocate(CHANNELS * native.FO_MAX_PEERS * 4, zero=True)
         self._next_channel = 0
@@ -97,6 +100,7 @@ class PeerGroup:
     def allocate(self, nbytes: int, zero: bool = False) -> SymmBuffer:
         """Collective: every rank must call with the same size, in the same order."""
         nbytes = (int(nbytes) + 255) // 256 * 256
+        self.symmetric_bytes += nbytes
         if self.world == 1:
             t = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
             if zero:

@@ -199,7 +199,7 @@ def test_fused_ddp_two_shot_matches_nccl_ddp():
     run_distributed(_ddp_worker, world_size=2, backend="nccl", args=(True,))
 
 
-def _fsdp_worker(rank, world, staged=False):
+def _fsdp_worker(rank, world, staged=False, ag_copy_engine=False):
     from torch.distributed.fsdp import fully_shard
 
     from flashoptim_b200 import FlashAdamW, FlashLion, enable_gradient_release
@@ -221,7 +221,9 @@ def _fsdp_worker(rank, world, staged=False):
             o1 = cls(plain.parameters(), **kw)
             o2 = cls(fused.parameters(), **kw)
             own_ag = release  # half of the cases also use the library's all-gather kernel
-            state = enable_fused_fsdp(fused, o2, own_all_gather=own_ag, staged=staged, max_ctas=2 if staged else 0)
+            own_ag = own_ag or ag_copy_engine
+            state = enable_fused_fsdp(fused, o2, own_all_gather=own_ag, staged=staged, max_ctas=2 if staged else 0,
+                                      all_gather_copy_engine=ag_copy_engine)
             if release:
                 enable_gradient_release(plain, o1)
                 enable_gradient_release(fused, o2)
@@ -247,6 +249,11 @@ def _fsdp_worker(rank, world, staged=False):
 
 def test_fused_fsdp_matches_nccl_fsdp():
     run_distributed(_fsdp_worker, world_size=2, backend="nccl")
+
+
+def test_fused_fsdp_copy_engine_all_gather():
+    """FSDP2's parameter all-gather as copy-engine pulls between two flag kernels."""
+    run_distributed(_fsdp_worker, world_size=2, backend="nccl", args=(False, True))
 
 
 def test_fused_fsdp_staged_kernels_match_nccl_fsdp():
