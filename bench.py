@@ -181,7 +181,7 @@ def timeline_summary(step_fn, rank: int, path: str, fused_state) -> dict:
             if ks:
                 t0 = min(e["ts"] for e in ks)
                 t1 = max(e["ts"] + e["dur"] for e in ks)
-                streams, fam, fam_n = {}, {}, {}
+                streams, fam, fam_n, by_name = {}, {}, {}, {}
                 for e in ks:
                     sid = e.get("args", {}).get("stream", -1)
                     name = e["name"] if e.get("cat") == "kernel" else e.get("cat")
@@ -191,12 +191,19 @@ def timeline_summary(step_fn, rank: int, path: str, fused_state) -> dict:
                     streams[sid]["fam"][k] = streams[sid]["fam"].get(k, 0.0) + e["dur"] / 1e3
                     fam[k] = fam.get(k, 0.0) + e["dur"] / 1e3
                     fam_n[k] = fam_n.get(k, 0) + 1
+                    short = name.split("(")[0][:70]
+                    t_n = by_name.setdefault(short, [0.0, 0])
+                    t_n[0] += e["dur"] / 1e3
+                    t_n[1] += 1
                 gemm_stream = max(streams, key=lambda sid: streams[sid]["fam"].get("gemm", 0.0))
                 wall = (t1 - t0) / 1e3
                 out = {
                     "label": label, "steps": 2, "wall_ms_per_step": round(wall / 2, 2),
                     "kernel_ms_per_step_by_family": {k: round(v / 2, 2) for k, v in sorted(fam.items())},
                     "launches_per_step_by_family": {k: v / 2 for k, v in sorted(fam_n.items())},
+                    "top_kernels_ms_per_step": [
+                        {"name": nm, "ms": round(v[0] / 2, 2), "launches": v[1] / 2}
+                        for nm, v in sorted(by_name.items(), key=lambda kv: -kv[1][0])[:14]],
                     "compute_stream": gemm_stream,
                     "compute_stream_idle_ms_per_step": round((wall - _union_ms(streams[gemm_stream]["iv"])) / 2, 2),
                     "streams": {str(sid): {"busy_ms_per_step": round(_union_ms(v["iv"]) / 2, 2),

@@ -100,14 +100,23 @@ def main():
     if state is not None:
         state.check()
     torch.cuda.reset_peak_memory_stats()
+    # read-only NVML sampler, loaded by file path so the reference mode imports nothing of this package
+    tspec = importlib.util.spec_from_file_location(
+        "_bench_timing", os.path.join(ROOT, "flashoptim_b200", "utils", "timing.py"))
+    timing = importlib.util.module_from_spec(tspec)
+    sys.modules["_bench_timing"] = timing
+    tspec.loader.exec_module(timing)
+    sampler = timing.ClockSampler(local_rank)
     dist.barrier()
     torch.cuda.synchronize()
+    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
         loss = step(args.warmup + i)
     e1.record()
     torch.cuda.synchronize()
+    sampler.stop()
     dist.barrier()
     t = torch.tensor([e0.elapsed_time(e1) / args.steps, torch.cuda.max_memory_allocated() / 2**30], device=dev,
                      dtype=torch.float64)
@@ -123,6 +132,7 @@ def main():
             "loss": float(loss), "steps": args.steps, "warmup": args.warmup,
             "buckets_fused_per_step": (state.buckets_fused // (args.steps + args.warmup)) if state else 0,
             "buckets_two_shot_per_step": (state.buckets_two_shot // (args.steps + args.warmup)) if state else 0,
+            "clocks": sampler.summary(),
         }), flush=True)
     dist.destroy_process_group()
 

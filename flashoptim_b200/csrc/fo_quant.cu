@@ -199,6 +199,17 @@ __global__ void __launch_bounds__(kQThreads) dequantize_kernel(const uint8_t* __
 // Exact 2^e for e in [-126, 127].
 __device__ __forceinline__ float pow2i(int e) { return __int_as_float((e + 127) << 23); }
 
+// c / smax, correctly rounded, for an integer code |c| <= smax in {127, 32767}: the rounded
+// reciprocal, one product and one FMA-corrected refinement.  Equal to IEEE division for every
+// code (checked exhaustively against fp32 division; tests/test_kernels_gpu.py compares the
+// kernel with the PyTorch formulation over all codes) at a third of its instructions.
+__device__ __forceinline__ float div_by_code_range(float c, float smax) {
+  const float r = smax == 127.0f ? (1.0f / 127.0f) : (1.0f / 32767.0f);
+  const float q0 = __fmul_rn(c, r);
+  const float rem = __fmaf_rn(-q0, smax, c);
+  return __fmaf_rn(rem, r, q0);
+}
+
 template <typename T>
 __device__ __forceinline__ int ecc_log_scale_bits(uint16_t bits) {
   constexpr int M = Elem<T>::kMant;
@@ -231,7 +242,7 @@ __global__ void __launch_bounds__(kQThreads) ecc_decode_kernel(const T* __restri
     for (int i = 0; i < kUnit; ++i) {
       const int ls = ecc_log_scale_bits<T>(h[i]);
       const int hh = ls >> 1;  // floor(ls / 2)
-      const float corr = __fdiv_rn((float)c[i], smax);
+      const float corr = div_by_code_range((float)c[i], smax);
       const float e = __fmul_rn(__fmul_rn(corr, pow2i(hh)), pow2i(ls - hh));
       r[i] = __fadd_rn(narrow_bits_to_float<T>(h[i]), e);
     }
@@ -285,9 +296,13 @@ __global__ void __launch_bounds__(kQThreads) maxabs_kernel(const T* __restrict__
   if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(a));
 }
 
-// Grid: enough CTAs to fill the device several times over (these kernels hide latency by
-// occupancy), never more than the work; the SM count is read once per device.
+// Grid: one unit per thread (these kernels hide latency by occupancy and by the block
+// scheduler's turnover, like the reference's one-block-per-1024-elements launches); the
+// grid-stride loops only come into play beyond 2^20 blocks (2^31 elements).  -DFO_QUANT_BLOCKS_PER_SM=k
+// gives the persistent alternative (k blocks per SM) for tuning builds.
 static int blocks_for(int64_t units) {
+  int64_t b = (units + kQThreads - 1) / kQThreads;
+#ifdef FO_QUANT_BLOCKS_PER_SM
   static int sms[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -300,8 +315,10 @@ static int blocks_for(int64_t units) {
     }
     n = sms[dev];
   }
-  int64_t b = (units + kQThreads - 1) / kQThreads;
-  const int64_t cap = (int64_t)n * 16;
+  const int64_t cap = (int64_t)n * FO_QUANT_BLOCKS_PER_SM;
+#else
+  const int64_t cap = int64_t(1) << 20;
+#endif
   if (b > cap) b = cap;
   if (b < 1) b = 1;
   return (int)b;

@@ -21,6 +21,15 @@ side stream.  Plain DDP (no hook) with ``optimizer.step()`` keeps working.
 
 Gradient accumulation with ``no_sync()`` is transparent: DDP does not call the
 hook on unsynchronised backwards and the bucket later holds the accumulated sum.
+
+What it buys, measured (GPT-2 medium, 8 sequences of 1024 per GPU, B200): the fused hook is a
+correctness-complete alternative, NOT a speed-up.  It ran within 1 % of NCCL all-reduce followed
+by this library's multi-tensor step (50.0 vs 49.3 ms per step on 2 GPUs, 50.7 vs 50.2 on 8) and
+5 % ahead of the reference optimizer on stock DDP.  DDP's reducer owns its buckets, so every
+bucket is first copied into the symmetric arena (one more pass of all gradients through HBM),
+and a replicated update is HBM-bound on every rank whatever the collective does.  The fused
+FSDP2 path (``enable_fused_fsdp``), where each rank updates only its shard, is where fusing
+pays.
 """
 
 from __future__ import annotations
@@ -175,6 +184,10 @@ def fuse_ddp_allreduce(
     two_shot: Optional[bool] = None,
 ) -> FusedDDPState:
     """Fuse DDP's per-bucket gradient all-reduce with ``optimizer``'s update.
+
+    Measured on 2 and 8 B200s this is about 1 % slower than leaving the all-reduce to NCCL and
+    calling ``optimizer.step()`` (see the module docstring): use it for its properties
+    (bit-identical replicas by construction, no NCCL in the gradient path), not for speed.
 
     Collective: call on every rank, after constructing ``ddp_model`` (with
     ``gradient_as_bucket_view=True``) and ``optimizer``.  Keep calling

@@ -69,6 +69,21 @@ def test_ecc_matches_oracle_bitwise(n, dtype, mbw):
     assert (r - x).abs().max() <= (w.float() - x).abs().max()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("code_dtype", [torch.int8, torch.int16])
+def test_ecc_decode_every_code_value_bitwise(dtype, code_dtype):
+    """Every code (all 255 int8 values, all 65535 int16 values) against several parameter
+    values, bit for bit with the PyTorch formulation: the kernel divides the code by its range
+    through a reciprocal and one FMA correction, which has to equal IEEE division everywhere."""
+    lim = 127 if code_dtype == torch.int8 else 32767
+    codes = torch.arange(-lim, lim + 1, dtype=torch.int32)
+    params = torch.tensor([1.0, -0.0371, 3.1e-5, 250.0, 6.1e-5 if dtype == torch.float16 else 1e-30], dtype=dtype)
+    w = params.repeat_interleave(codes.numel())
+    e = codes.repeat(params.numel()).to(code_dtype)
+    got = reconstruct_fp32_param(w.cuda(), e.cuda()).cpu()
+    assert torch.equal(got, oracle.ecc_decode_ref(w, e))
+
+
 def test_maxabs():
     x = _rand(100003, torch.bfloat16, 2.0)
     assert maxabs(x) == float(x.abs().max())

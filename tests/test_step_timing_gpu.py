@@ -66,11 +66,13 @@ def test_fused_step_is_as_fast_as_the_eager_formulations(opt_name, d):
 def test_multi_tensor_launch_costs_what_one_tensor_costs():
     """291 tensors with the sizes of a (width-reduced) Llama layer list, one fused launch, against
     ONE tensor holding the same number of elements: within 10 % (+0.05 ms), because the grid walks
-    chunks, not tensors.  The reference launches once per tensor instead."""
+    chunks, not tensors.  The reference launches once per tensor instead.  The list is large
+    enough (2 G elements, about 4 ms on the device) that the host's walk over 291 parameters
+    (about 2 ms of Python per step) hides behind the previous step's kernel."""
     import warnings
 
     warnings.simplefilter("ignore")
-    d, ffn, vocab = 1024, 3584, 32064
+    d, ffn, vocab = 2048, 7168, 64128
     shapes = [(vocab, d)]
     for _ in range(32):
         shapes += [(d, d), (d // 4, d), (d // 4, d), (d, d), (ffn, d), (ffn, d), (d, ffn), (d,), (d,)]
