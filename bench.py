@@ -84,12 +84,16 @@ def parse_args():
                     help="fused path: FSDP2's parameter all-gather through this library's pull kernel")
     ap.add_argument("--all-gather", default="auto", choices=["auto", "copy_engine", "nccl"],
                     help="fused path: copy_engine = FSDP2's parameter all-gather as cudaMemcpyAsync pulls between "
-                         "two flag kernels (no SM, three group-sized buffers); auto: all-gather on write where "
-                         "--push-params allows, else NCCL")
+                         "two flag kernels (no SM, three group-sized buffers), the default; nccl = FSDP2's own")
+    ap.add_argument("--oversized-groups", default="nccl", choices=["nccl", "fused"],
+                    help="fused path: a parameter group more than twice the typical size (embedding + output "
+                         "head) keeps FSDP2's NCCL collectives, so the pooled symmetric buffers stay layer-sized "
+                         "(nccl, default), or is served too (fused)")
     ap.add_argument("--push-params", default="auto", choices=["auto", "on", "off"],
                     help="fused path: the update kernel also stores the new parameters into every rank's "
-                         "all-gather buffer, so FSDP2's parameter all-gathers move no data; auto = on at "
-                         "2 GPUs (the size it has been measured at), off otherwise")
+                         "all-gather buffer, so FSDP2's parameter all-gathers move no data (1-2 % faster than the "
+                         "copy-engine all-gather, at the price of an unsharded copy of the parameters per GPU); "
+                         "auto = off (the copy-engine all-gather keeps peak memory where FSDP2's own is)")
     ap.add_argument("--push-budget-gb", type=float, default=0.0,
                     help="with the parameter push: GiB of persistent all-gather buffers per GPU (0: every group)")
     ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
@@ -327,7 +331,8 @@ def main():
     if args.impl == "ours" and world > 1:
         from flashoptim_b200.parallel import tuned_options
 
-        tuned = tuned_options(world, n_params * 2)  # bf16 parameters
+        # bf16 parameters; --push-params on grants the memory for the all-gather on write
+        tuned = tuned_options(world, n_params * 2, push_budget_bytes=(1 << 62) if args.push_params == "on" else 0)
     staged = tuned.get("staged", False) if args.comm_kernel == "auto" else args.comm_kernel == "staged"
     transport = "kernel" if args.transport == "auto" else args.transport
     use_multicast = tuned.get("use_multicast", False) if args.multicast == "auto" else args.multicast == "on"
@@ -341,6 +346,8 @@ def main():
     own_ag = args.own_all_gather or ag_ce
     if own_ag and args.push_params != "on":
         push_params = False
+    if push_params and args.all_gather == "auto" and args.push_budget_gb > 0:
+        own_ag = ag_ce = True  # groups beyond the push budget: copy-engine all-gather instead of NCCL
     if args.sweep:  # every variant must be reachable by flipping switches at run time
         use_multicast, push_params, own_ag = True, True, True
     if args.impl == "ours" and args.fused_comm == "auto":
@@ -351,7 +358,7 @@ def main():
                                                     use_multicast=use_multicast, own_all_gather=own_ag,
                                                     all_gather_copy_engine=ag_ce,
                                                     push_params=push_params, staged=staged, push_multicast=push_mc,
-                                                    transport=transport,
+                                                    transport=transport, oversized_groups=args.oversized_groups,
                                                     push_budget_bytes=int(args.push_budget_gb * 2**30) or None)
             fused_comm = fused_state is not None
         except Exception as e:  # the plain path is always available
@@ -611,6 +618,7 @@ def main():
                 "fused_comm_ctas": comm_ctas if fused_comm else None,
                 "fused_comm_kernel": ("staged" if staged else "register") if fused_comm else None,
                 "fused_comm_transport": transport if fused_comm else None,
+                "fused_oversized_groups": args.oversized_groups if fused_comm else None,
                 "fused_all_gather": (fused_state.all_gather_mode + ("/copy_engine" if fused_state.ag_copy_engine and
                                      fused_state.all_gather_mode == "pull" else "")) if fused_comm else None,
                 **({"fused_comm_error": fused_error} if fused_error else {}),

@@ -358,7 +358,9 @@ class FusedFSDPState:
     def __init__(self, model: nn.Module, optimizer: FlashOptimizer, group, timeout_s, use_multicast, depth,
                  max_ctas=0, own_all_gather=False, push_params=False, push_budget_bytes=None,
                  last_group_full_grid=True, staged=False, push_multicast=None, transport="kernel",
-                 all_gather_copy_engine=False):
+                 all_gather_copy_engine=False, oversized_groups="nccl"):
+        if oversized_groups not in ("nccl", "fused"):
+            raise ValueError(f"oversized_groups must be 'nccl' or 'fused', got {oversized_groups!r}")
         self.optimizer = optimizer
         self.ag_copy_engine = bool(all_gather_copy_engine)  # own_all_gather: copy engines, not the pull kernel
         if transport not in ("kernel", "copy_engine"):
@@ -381,14 +383,25 @@ class FusedFSDPState:
         self.fused_calls = 0
         self.fallbacks = 0
         self.comms = []
-        need = 0
+        sizes = []
         for m, pg in groups:
             comm = FusedReduceScatter(self, list(pg.fsdp_params), pg)
-            need = max(need, comm.input_numel * torch.empty((), dtype=comm.dtype).element_size())
+            sizes.append(comm.input_numel * torch.empty((), dtype=comm.dtype).element_size())
             self.comms.append((m, comm))
+        # The symmetric buffers are pools sized by the largest group they serve.  A group much
+        # larger than the typical one (a model's embedding + output head beside its layers)
+        # would multiply every pool buffer: with oversized_groups="nccl" such a group keeps
+        # FSDP2's own collectives (it is reduced last and gathered first, where nothing overlaps
+        # anyway) and the pools stay at the size of a layer.
+        typical = sorted(sizes)[len(sizes) // 2]
+        self.oversized = [n > 2 * typical for n in sizes] if oversized_groups == "nccl" else [False] * len(sizes)
+        for (m, comm), big in zip(self.comms, self.oversized):
+            if big:
+                comm.supported = False
+        need = max([n for n, big in zip(sizes, self.oversized) if not big] or [0])
         # modules() lists the outermost module first; its group holds what the model applies
         # first and is therefore the one whose gradients backward completes last
-        if last_group_full_grid and len(self.comms) > 1:
+        if last_group_full_grid and len(self.comms) > 1 and not self.oversized[0]:
             self.comms[0][1].full_grid = True
         self.pool_bytes = need
         self.pool = _Pool(self.peers, need, depth)
@@ -430,7 +443,7 @@ class FusedFSDPState:
             # three buffers: one being copied out, one prefetched, one spare
             self.ag_pool_bytes = need
             self.ag_pool = _Pool(self.peers, need, 3)
-            self._pull_installs = [(m, PeerAllGather(self)) for m, _ in groups]
+            self._pull_installs = [(m, PeerAllGather(self)) for (m, _), big in zip(groups, self.oversized) if not big]
         for m, comm in self.comms:
             m.set_custom_reduce_scatter(comm)
         self._installs: list[tuple[nn.Module, object]] = []
@@ -497,31 +510,27 @@ class FusedFSDPState:
         self.peers.poll_status()
 
 
-# All-gather on write keeps one unsharded copy of the parameters on every GPU; tuned_options()
-# proposes it while that copy stays below this many bytes.
-PUSH_AUTO_MAX_BYTES = 24 * 2**30
+def tuned_options(world_size: int, unsharded_param_bytes: int = 0, push_budget_bytes: int = 0) -> dict:
+    """Keyword arguments for :func:`enable_fused_fsdp` that measured best for Llama-3-8B / 70B
+    training steps on 2, 4 and 8 B200s of one NVSwitch node (``bench.py --sweep``; the tables
+    are in ``profiles/fsdp2_llama8b_collective_paths_sweep.md``).
 
-
-def tuned_options(world_size: int, unsharded_param_bytes: int = 0) -> dict:
-    """Keyword arguments for :func:`enable_fused_fsdp` that measured best for Llama-3-8B training
-    steps on 2, 4 and 8 B200s of one NVSwitch node (``bench.py --sweep``; the tables are in the
-    repository's design notes).
-
-    * Two ranks: the kernel is bound by its own arithmetic and HBM, not by the link; the
+    * Two ranks: the kernel is bound by its own arithmetic and HBM traffic, not by the link; the
       bulk-copy staged kernel on the whole GPU finishes soonest, parameters are pushed with one
       store per rank.
     * More ranks: NVLink-bound.  ``multimem.ld_reduce`` lets the switch add the ranks' copies,
-      four units per thread are in flight, and 48 CTAs keep the links busy while the other SMs
-      stay with backward's GEMMs; parameters are pushed with ``multimem.st``.
-    * ``push_params`` (all-gather on write) is proposed when ``unsharded_param_bytes`` is given
-      and at most :data:`PUSH_AUTO_MAX_BYTES`; otherwise FSDP2's parameter all-gather is done by
-      the copy engines (``own_all_gather`` + ``all_gather_copy_engine``), which costs three
-      group-sized buffers."""
+      four units per thread are in flight, and 64 (3-4 ranks) or 48 (5-8 ranks) CTAs keep the
+      links busy while the other SMs stay with backward's GEMMs; ``multimem.st`` for pushes.
+    * Parameter all-gather: by the copy engines (``own_all_gather`` + ``all_gather_copy_engine``:
+      no SM, three group-sized buffers, so peak memory stays where FSDP2's own is).  The
+      all-gather on write (``push_params``) is 1-2 % faster still but keeps an unsharded copy
+      of the parameters on every GPU (16 GB for 8 B parameters); it is proposed only when that
+      copy, ``unsharded_param_bytes``, fits the ``push_budget_bytes`` the caller grants."""
     if world_size <= 2:
         opts = dict(use_multicast=False, staged=True, max_ctas=0, push_multicast=False)
     else:
-        opts = dict(use_multicast=True, staged=False, max_ctas=48, push_multicast=True)
-    if 0 < unsharded_param_bytes <= PUSH_AUTO_MAX_BYTES:
+        opts = dict(use_multicast=True, staged=False, max_ctas=64 if world_size <= 4 else 48, push_multicast=True)
+    if 0 < unsharded_param_bytes <= push_budget_bytes:
         opts["push_params"] = True
     else:
         opts.update(own_all_gather=True, all_gather_copy_engine=True)
@@ -545,6 +554,7 @@ def enable_fused_fsdp(
     push_multicast: Optional[bool] = None,
     transport: str = "kernel",
     all_gather_copy_engine: bool = False,
+    oversized_groups: str = "nccl",
 ) -> Optional[FusedFSDPState]:
     """Fuse FSDP2's gradient reduce-scatter with ``optimizer``'s sharded update.
 
@@ -577,6 +587,10 @@ def enable_fused_fsdp(
     parameters go to the peers' all-gather buffers in further copy-engine copies.  It costs one
     more pass of the gradients through HBM and one local ``[world, shard]`` staging buffer, and
     leaves every SM to backward's GEMMs while the links are busy.
+    ``oversized_groups="nccl"`` (default) leaves a parameter group that is more than twice the
+    size of the typical one (an embedding + output head beside transformer layers) to FSDP2's own
+    collectives, so that the pooled symmetric buffers have the size of a layer; ``"fused"`` serves
+    it too and sizes every pool buffer for it.
     ``own_all_gather`` also replaces FSDP2's parameter all-gather by this library's own over
     symmetric buffers (:class:`PeerAllGather`): a pull kernel, or with ``all_gather_copy_engine``
     one ``cudaMemcpyAsync`` per peer, which takes no SM from the GEMMs it overlaps and costs
@@ -594,7 +608,7 @@ def enable_fused_fsdp(
     try:
         state = FusedFSDPState(model, optimizer, group, timeout_s, use_multicast, depth, max_ctas, own_all_gather,
                                push_params, push_budget_bytes, last_group_full_grid, staged, push_multicast, transport,
-                               all_gather_copy_engine)
+                               all_gather_copy_engine, oversized_groups)
     except UnsupportedFSDPInternals as e:
         # same PyTorch on every rank, so every rank lands here together, before any collective
         import warnings
