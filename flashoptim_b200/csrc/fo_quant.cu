@@ -296,13 +296,14 @@ __global__ void __launch_bounds__(kQThreads) maxabs_kernel(const T* __restrict__
   if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(a));
 }
 
-// Grid: one unit per thread (these kernels hide latency by occupancy and by the block
-// scheduler's turnover, like the reference's one-block-per-1024-elements launches); the
-// grid-stride loops only come into play beyond 2^20 blocks (2^31 elements).  -DFO_QUANT_BLOCKS_PER_SM=k
-// gives the persistent alternative (k blocks per SM) for tuning builds.
+// Grid: a persistent loop over 16 CTAs per SM (the SM count is read once per device), never
+// more than the work.  One unit per thread over the whole grid, like the reference's
+// one-block-per-1024-elements launches, was measured too: slower for three of the four
+// master-weight kernels (-DFO_QUANT_BLOCKS_PER_SM=k changes the factor for tuning builds).
+#ifndef FO_QUANT_BLOCKS_PER_SM
+#define FO_QUANT_BLOCKS_PER_SM 16
+#endif
 static int blocks_for(int64_t units) {
-  int64_t b = (units + kQThreads - 1) / kQThreads;
-#ifdef FO_QUANT_BLOCKS_PER_SM
   static int sms[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -315,10 +316,8 @@ static int blocks_for(int64_t units) {
     }
     n = sms[dev];
   }
+  int64_t b = (units + kQThreads - 1) / kQThreads;
   const int64_t cap = (int64_t)n * FO_QUANT_BLOCKS_PER_SM;
-#else
-  const int64_t cap = int64_t(1) << 20;
-#endif
   if (b > cap) b = cap;
   if (b < 1) b = 1;
   return (int)b;

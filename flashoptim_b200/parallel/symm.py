@@ -208,7 +208,9 @@ class PeerGroup:
                 self._poll = None
                 st = host.tolist()
                 if st[0] != 0:
-                    self.status.zero_()
+                    # only the two report words: the CTA counters behind them belong to kernels
+                    # that may be in flight
+                    self.status[:2].zero_()
                     raise CommTimeoutError(
                         f"rank {self.rank}: wait on channel mask {st[0]:#x} timed out (missing rank {st[1] - 1})"
                     )
