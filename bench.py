@@ -530,10 +530,12 @@ def main():
         torch.cuda.synchronize()
         reps = 10
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+        h0 = time.perf_counter()
         ev[0].record()
         for k in range(reps):
             opt.step()
             ev[k + 1].record()
+        step_host_ms = (time.perf_counter() - h0) * 1e3 / reps  # time the host needs to issue one step
         torch.cuda.synchronize()
         times = sorted(ev[k].elapsed_time(ev[k + 1]) for k in range(reps))
         opt.zero_grad(set_to_none=True)
@@ -550,10 +552,12 @@ def main():
             "step_ms": round(step_ms, 3),
             "step_ms_per_1b": round(step_ms / (local_elems / 1e9), 3),
             "step_hbm_frac": round(bytes_per_elem * local_elems / (step_ms * 1e-3) / (measured_hbm_gbs() * 1e9), 3),
+            "step_host_ms": round(step_host_ms, 3),
             "step_local_params": local_elems,
             "step_bytes_per_param": bytes_per_elem,
             "step_timing": f"median of {reps} optimizer.step() calls, CUDA events, max over ranks; HBM fraction of "
-                           f"the measured copy bandwidth {measured_hbm_gbs()} GB/s",
+                           f"the measured copy bandwidth {measured_hbm_gbs()} GB/s; when step_host_ms is not well below "
+                           "step_ms the loop is bound by the host's walk over the parameter list, not by the kernel",
         }
 
     timeline = None

@@ -303,6 +303,13 @@ class PushedAllGather(AllGather):  # type: ignore[misc,valid-type]
         return dist.all_gather_into_tensor(output_tensor, input_tensor, group=group, async_op=async_op)
 
 
+def oversized_mask(sizes: list[int]) -> list[bool]:
+    """Which groups are more than twice the size of the typical (median) group: a model's
+    embedding + output head beside its transformer layers."""
+    typical = sorted(sizes)[len(sizes) // 2]
+    return [n > 2 * typical for n in sizes]
+
+
 def select_push_groups(sizes: list[int], budget_bytes: Optional[int]) -> list[bool]:
     """Which groups get a persistent all-gather buffer: all supported ones (size > 0) without
     a budget, else in module order as long as their buffers fit into ``budget_bytes`` (the
@@ -393,8 +400,7 @@ class FusedFSDPState:
         # would multiply every pool buffer: with oversized_groups="nccl" such a group keeps
         # FSDP2's own collectives (it is reduced last and gathered first, where nothing overlaps
         # anyway) and the pools stay at the size of a layer.
-        typical = sorted(sizes)[len(sizes) // 2]
-        self.oversized = [n > 2 * typical for n in sizes] if oversized_groups == "nccl" else [False] * len(sizes)
+        self.oversized = oversized_mask(sizes) if oversized_groups == "nccl" else [False] * len(sizes)
         for (m, comm), big in zip(self.comms, self.oversized):
             if big:
                 comm.supported = False

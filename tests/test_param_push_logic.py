@@ -108,3 +108,26 @@ def test_poll_status_reports_a_timeout_one_call_late_without_waiting():
     assert int(peers.status[0]) == 0                 # cleared for the next use
     peers.poll_status()
     peers.poll_status()
+
+
+def test_oversized_groups_are_the_ones_far_above_the_median():
+    from flashoptim_b200.parallel.fsdp import oversized_mask
+
+    layer = 218_103_808 * 2
+    assert oversized_mask([5 * layer] + [layer] * 32) == [True] + [False] * 32   # Llama-3-8B: embedding + head
+    assert oversized_mask([layer] * 4) == [False] * 4
+    assert oversized_mask([256, 2080, 32896, 33280]) == [False] * 4              # nothing beyond twice the median
+    assert oversized_mask([7]) == [False]
+
+
+def test_tuned_options_by_world_size_and_memory_grant():
+    from flashoptim_b200.parallel import tuned_options
+
+    two = tuned_options(2, 16 << 30)
+    assert two["staged"] and not two["use_multicast"] and two["max_ctas"] == 0
+    assert two["own_all_gather"] and two["all_gather_copy_engine"] and "push_params" not in two
+    four, eight = tuned_options(4), tuned_options(8)
+    assert four["use_multicast"] and four["max_ctas"] == 64 and eight["max_ctas"] == 48 and not eight["staged"]
+    granted = tuned_options(8, 16 << 30, push_budget_bytes=32 << 30)
+    assert granted["push_params"] and "own_all_gather" not in granted
+    assert "push_params" not in tuned_options(8, 140 << 30, push_budget_bytes=32 << 30)  # does not fit the grant

@@ -118,8 +118,10 @@ def _noop_step(kind, p, ecc, err_bytes):
 
 @pytest.mark.parametrize("kind", ["adam", "momentum"])
 @pytest.mark.parametrize("dtype,fields", [
-    (torch.bfloat16, [1, 2, 24, 64, 100, 120, 126, 127, 128, 140, 200, 252, 253]),
-    (torch.float16, [127 - 24, 127 - 15, 127 - 14, 127 - 1, 127, 127 + 15]),
+    (torch.bfloat16, [1, 2, 24, 64, 100, 120, 126, 127, 128, 140, 200, 251, 252]),  # 253 rounds up to 2^127
+    # fp16: subnormals, the smallest normals, around one, and 2^14; in the top binade the master
+    # value 65504 + half a spacing narrows to infinity, here as in the reference's recipe
+    (torch.float16, [127 - 24, 127 - 15, 127 - 14, 127 - 1, 127, 127 + 14]),
 ])
 @pytest.mark.parametrize("err_bytes", [1, 2])
 def test_a_step_that_changes_nothing_keeps_every_master_value(kind, dtype, fields, err_bytes):
