@@ -19,6 +19,12 @@ all-gather output, so the parameter all-gathers of the following forward and bac
 passes move no data: they wait for the ranks' "pushed" flags and return
 (:class:`PushedAllGather`).  The price is one unsharded copy of the parameters per rank.
 
+Where that copy is too much, ``own_all_gather=True, all_gather_copy_engine=True`` keeps FSDP2's
+all-gather but performs it with ``cudaMemcpyAsync`` pulls between two one-CTA flag kernels
+(:class:`PeerAllGather`): the copy engines move the bytes and no SM is taken from the GEMMs that
+the all-gather overlaps, which is where NCCL's all-gather costs a training step most.
+:func:`tuned_options` returns the combination that measured best for a given number of GPUs.
+
 Parameters updated this way are skipped once by the next ``step()`` /
 ``step_param()``, so the usual training loop and gradient release keep working.
 Groups the kernel cannot serve (non-default divide factors, a reduce dtype
