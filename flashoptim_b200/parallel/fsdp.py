@@ -524,8 +524,8 @@ class FusedFSDPState:
 
 def tuned_options(world_size: int, unsharded_param_bytes: int = 0, push_budget_bytes: int = 0) -> dict:
     """Keyword arguments for :func:`enable_fused_fsdp` that measured best for Llama-3-8B / 70B
-    training steps on 2, 4 and 8 B200s of one NVSwitch node (``bench.py --sweep``; the tables
-    are in ``profiles/fsdp2_llama8b_collective_paths_sweep.md``).
+    training steps on 2, 4 and 8 B200s of one NVSwitch node (every path timed in one process with
+    ``bench.py --sweep``).
 
     * Two ranks: the kernel is bound by its own arithmetic and HBM traffic, not by the link; the
       bulk-copy staged kernel on the whole GPU finishes soonest, parameters are pushed with one
