@@ -14,11 +14,42 @@
 namespace fo {
 
 constexpr int kQThreads = 256;
+// Register budgets (launch bounds) that measured best on B200: 32 registers (8 CTAs per SM) for
+// the quantiser and dequantiser, 40 (6 CTAs, nothing spilled) for the master-weight kernels.
+constexpr int kQuantMinBlocks = 8;
+constexpr int kEccMinBlocks = 6;
 
-// Every kernel here gives a thread one unit of 8 consecutive elements per iteration and moves
-// it with 16-byte (8-byte for byte-sized elements) vector accesses when the tensor's base
-// address allows and the unit is whole; tails and unaligned tensors go element by element.
-// The arithmetic per element is the same in both paths.
+// ---------------------------------------------------------------- memory access
+// Read-once data through the non-coherent path with default caching: measured 2-3 % faster in
+// these kernels than L1::no_allocate loads.
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint2 ldg8(const void* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
+__device__ __forceinline__ uint32_t ldg4(const void* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
+
+// 256-bit accesses (sm_100 and later): a unit of eight fp32 values is one request.
+struct Words8 {
+  uint32_t w[8];
+};
+__device__ __forceinline__ bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; }
+__device__ __forceinline__ Words8 ldg32(const void* p) {
+  Words8 v;
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]), "=r"(v.w[6]),
+                 "=r"(v.w[7])
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st32(void* p, const Words8& v) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]),
+               "r"(v.w[3]), "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]), "r"(v.w[7])
+               : "memory");
+}
+
+// The quantiser and dequantiser give a thread one unit of 8 consecutive elements per iteration
+// (four lanes form a group of 32) and move it with vector accesses when the tensor's base
+// address allows and the unit is whole: 32 bytes for fp32 (two 16-byte requests when the unit
+// is only 16-byte aligned), 16 for 2-byte and 8 for 1-byte elements.  Tails and unaligned
+// tensors go element by element.  The arithmetic per element is the same in both paths.
 
 template <typename T>
 __device__ __forceinline__ float load_as_float(const T* p, int64_t i) {
@@ -38,11 +69,17 @@ template <typename T>
 __device__ __forceinline__ void load8f(const T* p, int64_t base, int64_t n, bool vec, float (&v)[kUnit]) {
   if (vec && base + kUnit <= n) {
     if constexpr (sizeof(T) == 4) {
-      const uint4 a = ld16_stream(p + base), b = ld16_stream(p + base + 4);
-      v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
-      v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y); v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+      if (aligned32(p + base)) {
+        const Words8 a = ldg32(p + base);
+#pragma unroll
+        for (int i = 0; i < kUnit; ++i) v[i] = __uint_as_float(a.w[i]);
+      } else {
+        const uint4 a = ldg16(p + base), b = ldg16(p + base + 4);
+        v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
+        v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y); v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+      }
     } else {
-      const uint4 a = ld16_stream(p + base);
+      const uint4 a = ldg16(p + base);
       const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -61,51 +98,33 @@ __device__ __forceinline__ void load8f(const T* p, int64_t base, int64_t n, bool
     for (int i = 0; i < kUnit; ++i) v[i] = base + i < n ? load_as_float(p, base + i) : 0.0f;
   }
 }
-// 8 narrow elements, raw 16-bit patterns (for the exponent arithmetic of the correction).
-template <typename T>
-__device__ __forceinline__ void load8bits(const T* p, int64_t base, int64_t n, bool vec, uint16_t (&h)[kUnit]) {
-  static_assert(sizeof(T) == 2, "narrow types only");
-  if (vec && base + kUnit <= n) {
-    const uint4 a = ld16_stream(p + base);
-    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      h[2 * i] = (uint16_t)(w[i] & 0xffffu);
-      h[2 * i + 1] = (uint16_t)(w[i] >> 16);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < kUnit; ++i) h[i] = base + i < n ? reinterpret_cast<const uint16_t*>(p)[base + i] : (uint16_t)0;
-  }
-}
 __device__ __forceinline__ void store8f(float* p, int64_t base, int64_t n, bool vec, const float (&v)[kUnit]) {
   if (vec && base + kUnit <= n) {
-    st16(p + base, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])));
-    st16(p + base + 4,
-         make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7])));
+    if (aligned32(p + base)) {
+      Words8 o;
+#pragma unroll
+      for (int i = 0; i < kUnit; ++i) o.w[i] = __float_as_uint(v[i]);
+      st32(p + base, o);
+    } else {
+      st16(p + base, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])));
+      st16(p + base + 4,
+           make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7])));
+    }
   } else {
 #pragma unroll
     for (int i = 0; i < kUnit; ++i)
       if (base + i < n) p[base + i] = v[i];
   }
 }
-// 8 one-byte or two-byte integers (two's complement in the low bits of c[i]).
+// 8 one-byte integers (two's complement in the low bits of c[i]).
 template <typename E>
 __device__ __forceinline__ void store8i(E* p, int64_t base, int64_t n, bool vec, const int (&c)[kUnit]) {
+  static_assert(sizeof(E) == 1, "8-bit codes only");
   if (vec && base + kUnit <= n) {
-    if constexpr (sizeof(E) == 1) {
-      uint2 o;
-      o.x = (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)(c[3] & 0xff) << 24);
-      o.y = (c[4] & 0xff) | ((c[5] & 0xff) << 8) | ((c[6] & 0xff) << 16) | ((uint32_t)(c[7] & 0xff) << 24);
-      st8(p + base, o);
-    } else {
-      uint4 o;
-      o.x = (c[0] & 0xffff) | ((uint32_t)(c[1] & 0xffff) << 16);
-      o.y = (c[2] & 0xffff) | ((uint32_t)(c[3] & 0xffff) << 16);
-      o.z = (c[4] & 0xffff) | ((uint32_t)(c[5] & 0xffff) << 16);
-      o.w = (c[6] & 0xffff) | ((uint32_t)(c[7] & 0xffff) << 16);
-      st16(p + base, o);
-    }
+    uint2 o;
+    o.x = (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)(c[3] & 0xff) << 24);
+    o.y = (c[4] & 0xff) | ((c[5] & 0xff) << 8) | ((c[6] & 0xff) << 16) | ((uint32_t)(c[7] & 0xff) << 24);
+    st8(p + base, o);
   } else {
 #pragma unroll
     for (int i = 0; i < kUnit; ++i)
@@ -114,20 +133,14 @@ __device__ __forceinline__ void store8i(E* p, int64_t base, int64_t n, bool vec,
 }
 template <typename E>
 __device__ __forceinline__ void load8i(const E* p, int64_t base, int64_t n, bool vec, int (&c)[kUnit]) {
+  static_assert(sizeof(E) == 1, "8-bit codes only");
   if (vec && base + kUnit <= n) {
-    if constexpr (sizeof(E) == 1) {
-      const uint2 a = ld8_stream(p + base);
-      const uint32_t w[2] = {a.x, a.y};
+    const uint2 a = ldg8(p + base);
+    const uint32_t w[2] = {a.x, a.y};
 #pragma unroll
-      for (int i = 0; i < kUnit; ++i) {
-        const uint32_t b = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
-        c[i] = std::is_signed<E>::value ? (int)(int8_t)b : (int)b;
-      }
-    } else {
-      const uint4 a = ld16_stream(p + base);
-      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-      for (int i = 0; i < kUnit; ++i) c[i] = (int)(int16_t)((w[i >> 1] >> (16 * (i & 1))) & 0xffffu);
+    for (int i = 0; i < kUnit; ++i) {
+      const uint32_t b = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+      c[i] = std::is_signed<E>::value ? (int)(int8_t)b : (int)b;
     }
   } else {
 #pragma unroll
@@ -137,8 +150,8 @@ __device__ __forceinline__ void load8i(const E* p, int64_t base, int64_t n, bool
 
 // One thread per unit of 8 elements; four lanes form a group.
 template <typename T, bool kSigned, bool kSqrt, bool kSoftsign>
-__global__ void __launch_bounds__(kQThreads) quantize_kernel(const T* __restrict__ x, uint8_t* __restrict__ q,
-                                                             __half* __restrict__ scales, int64_t n) {
+__global__ void __launch_bounds__(kQThreads, kQuantMinBlocks)
+    quantize_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, __half* __restrict__ scales, int64_t n) {
   const int64_t n_units = ((n + kGroup - 1) / kGroup) * (kGroup / kUnit);
   const bool vec = aligned_for_units(x) && aligned_for_units(q);
   for (int64_t unit = (int64_t)blockIdx.x * kQThreads + threadIdx.x; unit - threadIdx.x < n_units;
@@ -171,9 +184,9 @@ __global__ void __launch_bounds__(kQThreads) quantize_kernel(const T* __restrict
 }
 
 template <bool kSigned, bool kSqrt, bool kSoftsign>
-__global__ void __launch_bounds__(kQThreads) dequantize_kernel(const uint8_t* __restrict__ q,
-                                                               const __half* __restrict__ scales,
-                                                               float* __restrict__ out, int64_t n) {
+__global__ void __launch_bounds__(kQThreads, kQuantMinBlocks)
+    dequantize_kernel(const uint8_t* __restrict__ q, const __half* __restrict__ scales, float* __restrict__ out,
+                      int64_t n) {
   const int64_t n_units = (n + kUnit - 1) / kUnit;
   const bool vec = aligned_for_units(q) && aligned_for_units(out);
   for (int64_t unit = (int64_t)blockIdx.x * kQThreads + threadIdx.x; unit < n_units;
@@ -195,6 +208,8 @@ __global__ void __launch_bounds__(kQThreads) dequantize_kernel(const uint8_t* __
     store8f(out, base, n, vec, r);
   }
 }
+
+// ---------------------------------------------------------------- master-weight split / merge
 
 // Exact 2^e for e in [-126, 127].
 __device__ __forceinline__ float pow2i(int e) { return __int_as_float((e + 127) << 23); }
@@ -224,57 +239,148 @@ __device__ __forceinline__ float narrow_bits_to_float(uint16_t bits) {
   else return __uint_as_float((uint32_t)bits << 16);
 }
 
-template <typename T, typename E>
-__global__ void __launch_bounds__(kQThreads) ecc_decode_kernel(const T* __restrict__ w, const E* __restrict__ ecc,
-                                                               float* __restrict__ out, int64_t n) {
-  const float smax = sizeof(E) == 1 ? 127.0f : 32767.0f;
-  const int64_t n_units = (n + kUnit - 1) / kUnit;
-  const bool vec = aligned_for_units(w) && aligned_for_units(ecc) && aligned_for_units(out);
-  for (int64_t unit = (int64_t)blockIdx.x * kQThreads + threadIdx.x; unit < n_units;
-       unit += (int64_t)gridDim.x * kQThreads) {
-    const int64_t base = unit * kUnit;
-    uint16_t h[kUnit];
-    int c[kUnit];
-    load8bits(w, base, n, vec, h);
-    load8i(ecc, base, n, vec, c);
-    float r[kUnit];
-#pragma unroll
-    for (int i = 0; i < kUnit; ++i) {
-      const int ls = ecc_log_scale_bits<T>(h[i]);
-      const int hh = ls >> 1;  // floor(ls / 2)
-      const float corr = div_by_code_range((float)c[i], smax);
-      const float e = __fmul_rn(__fmul_rn(corr, pow2i(hh)), pow2i(ls - hh));
-      r[i] = __fadd_rn(narrow_bits_to_float<T>(h[i]), e);
+// The split / merge kernels use an interleaved layout: a warp owns a tile of 256 consecutive
+// elements and a lane moves elements [4 * lane, 4 * lane + 4) of each half, so that every
+// warp-wide access covers one contiguous span (512 / 256 / 128 bytes for 4- / 2- / 1-byte
+// elements).  Measured against 8 consecutive elements per lane (32-byte fp32 accesses at a
+// 32-byte stride): 4-15 % faster.
+template <typename T>
+__device__ __forceinline__ bool aligned_for_quads(const T* p) {
+  return (reinterpret_cast<uintptr_t>(p) & (sizeof(T) * 4 - 1)) == 0;
+}
+// Four elements as sizeof(T) packed words; zero beyond n.
+template <typename T>
+__device__ __forceinline__ void load4raw(const T* p, int64_t base, int64_t n, bool vec, uint32_t (&w)[sizeof(T)]) {
+  if (vec && base + 4 <= n) {
+    if constexpr (sizeof(T) == 4) {
+      const uint4 a = ldg16(p + base);
+      w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    } else if constexpr (sizeof(T) == 2) {
+      const uint2 a = ldg8(p + base);
+      w[0] = a.x; w[1] = a.y;
+    } else {
+      w[0] = ldg4(p + base);
     }
-    store8f(out, base, n, vec, r);
+  } else {
+#pragma unroll
+    for (int k = 0; k < (int)sizeof(T); ++k) w[k] = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (base + i < n) {
+        if constexpr (sizeof(T) == 4) w[i] = reinterpret_cast<const uint32_t*>(p)[base + i];
+        else if constexpr (sizeof(T) == 2)
+          w[i >> 1] |= (uint32_t) reinterpret_cast<const uint16_t*>(p)[base + i] << (16 * (i & 1));
+        else w[0] |= (uint32_t) reinterpret_cast<const uint8_t*>(p)[base + i] << (8 * i);
+      }
+    }
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store4raw(T* p, int64_t base, int64_t n, bool vec, const uint32_t (&w)[sizeof(T)]) {
+  if (vec && base + 4 <= n) {
+    if constexpr (sizeof(T) == 4) st16(p + base, make_uint4(w[0], w[1], w[2], w[3]));
+    else if constexpr (sizeof(T) == 2) st8(p + base, make_uint2(w[0], w[1]));
+    else *reinterpret_cast<uint32_t*>(p + base) = w[0];
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (base + i < n) {
+        if constexpr (sizeof(T) == 4) reinterpret_cast<uint32_t*>(p)[base + i] = w[i];
+        else if constexpr (sizeof(T) == 2)
+          reinterpret_cast<uint16_t*>(p)[base + i] = (uint16_t)(w[i >> 1] >> (16 * (i & 1)));
+        else reinterpret_cast<uint8_t*>(p)[base + i] = (uint8_t)(w[0] >> (8 * i));
+      }
+    }
+  }
+}
+// Element i of a packed quad of signed codes as an exact float.  The caller has flipped the sign
+// bit of every code in the packed word (code + 128, or + 32768, as an unsigned field); one byte
+// permute drops that field into the mantissa of 2^23 and subtracting 2^23 + the offset leaves
+// the code: no integer-to-float conversion and no sign extension per element.
+template <typename E>
+__device__ __forceinline__ float quad_code_f(const uint32_t (&w)[sizeof(E)], int i) {
+  if constexpr (sizeof(E) == 1)
+    return __fsub_rn(__uint_as_float(__byte_perm(w[0], 0x4B000000u, 0x7440u | i)), 8388736.0f);
+  else
+    return __fsub_rn(__uint_as_float(__byte_perm(w[i >> 1], 0x4B000000u, (i & 1) ? 0x7432u : 0x7410u)), 8421376.0f);
+}
+
+template <typename T, typename E>
+__global__ void __launch_bounds__(kQThreads, kEccMinBlocks)
+    ecc_decode_kernel(const T* __restrict__ w, const E* __restrict__ ecc, float* __restrict__ out, int64_t n) {
+  const float smax = sizeof(E) == 1 ? 127.0f : 32767.0f;
+  const uint32_t flip = sizeof(E) == 1 ? 0x80808080u : 0x80008000u;
+  const bool vec = aligned_for_quads(w) && aligned_for_quads(ecc) && aligned_for_quads(out);
+  const int lane = threadIdx.x & 31;
+  const int64_t n_tiles = (n + 255) >> 8;
+  const int64_t n_warps = (int64_t)gridDim.x * (kQThreads / 32);
+  for (int64_t tile = ((int64_t)blockIdx.x * kQThreads + threadIdx.x) >> 5; tile < n_tiles; tile += n_warps) {
+    const int64_t b[2] = {tile * 256 + lane * 4, tile * 256 + 128 + lane * 4};
+    uint32_t wn[2][2], wc[2][sizeof(E)];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      load4raw(w, b[hf], n, vec, wn[hf]);
+      load4raw(ecc, b[hf], n, vec, wc[hf]);
+    }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+#pragma unroll
+      for (int k = 0; k < (int)sizeof(E); ++k) wc[hf][k] ^= flip;
+      uint32_t r[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint16_t hb = (uint16_t)(wn[hf][i >> 1] >> (16 * (i & 1)));
+        const int ls = ecc_log_scale_bits<T>(hb);
+        const int hh = ls >> 1;  // floor(ls / 2)
+        const float corr = div_by_code_range(quad_code_f<E>(wc[hf], i), smax);
+        const float e = __fmul_rn(__fmul_rn(corr, pow2i(hh)), pow2i(ls - hh));
+        r[i] = __float_as_uint(__fadd_rn(narrow_bits_to_float<T>(hb), e));
+      }
+      store4raw(out, b[hf], n, vec, r);
+    }
   }
 }
 
 template <typename T, typename E>
-__global__ void __launch_bounds__(kQThreads) ecc_encode_kernel(const float* __restrict__ x, const T* __restrict__ w,
-                                                               E* __restrict__ ecc, int64_t n) {
+__global__ void __launch_bounds__(kQThreads, kEccMinBlocks)
+    ecc_encode_kernel(const float* __restrict__ x, const T* __restrict__ w, E* __restrict__ ecc, int64_t n) {
   const float smax = sizeof(E) == 1 ? 127.0f : 32767.0f;
-  const int64_t n_units = (n + kUnit - 1) / kUnit;
-  const bool vec = aligned_for_units(x) && aligned_for_units(w) && aligned_for_units(ecc);
-  for (int64_t unit = (int64_t)blockIdx.x * kQThreads + threadIdx.x; unit < n_units;
-       unit += (int64_t)gridDim.x * kQThreads) {
-    const int64_t base = unit * kUnit;
-    uint16_t h[kUnit];
-    float xv[kUnit];
-    load8bits(w, base, n, vec, h);
-    load8f(x, base, n, vec, xv);
-    int c[kUnit];
+  const bool vec = aligned_for_quads(x) && aligned_for_quads(w) && aligned_for_quads(ecc);
+  const int lane = threadIdx.x & 31;
+  const int64_t n_tiles = (n + 255) >> 8;
+  const int64_t n_warps = (int64_t)gridDim.x * (kQThreads / 32);
+  for (int64_t tile = ((int64_t)blockIdx.x * kQThreads + threadIdx.x) >> 5; tile < n_tiles; tile += n_warps) {
+    const int64_t b[2] = {tile * 256 + lane * 4, tile * 256 + 128 + lane * 4};
+    uint32_t wn[2][2], wx[2][4];
 #pragma unroll
-    for (int i = 0; i < kUnit; ++i) {
-      const int neg = -ecc_log_scale_bits<T>(h[i]);
-      const int hh = neg >> 1;
-      const float e = __fsub_rn(xv[i], narrow_bits_to_float<T>(h[i]));
-      float en = __fmul_rn(__fmul_rn(e, pow2i(hh)), pow2i(neg - hh));
-      en = fminf(fmaxf(en, -1.0f), 1.0f);
-      const float s = __fmul_rn(en, smax);
-      c[i] = (int)copysignf(floorf(__fadd_rn(fabsf(s), 0.5f)), s);
+    for (int hf = 0; hf < 2; ++hf) {
+      load4raw(w, b[hf], n, vec, wn[hf]);
+      load4raw(x, b[hf], n, vec, wx[hf]);
     }
-    store8i(ecc, base, n, vec, c);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      uint32_t o[sizeof(E)];
+#pragma unroll
+      for (int k = 0; k < (int)sizeof(E); ++k) o[k] = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint16_t hb = (uint16_t)(wn[hf][i >> 1] >> (16 * (i & 1)));
+        const int neg = -ecc_log_scale_bits<T>(hb);
+        const int hh = neg >> 1;
+        const float e = __fsub_rn(__uint_as_float(wx[hf][i]), narrow_bits_to_float<T>(hb));
+        float en = __fmul_rn(__fmul_rn(e, pow2i(hh)), pow2i(neg - hh));
+        en = fminf(fmaxf(en, -1.0f), 1.0f);  // a NaN difference becomes -1
+        const float s = __fmul_rn(en, smax);
+        // copysign(floor(|s| + 0.5), s) without a float-to-int conversion: for 0 <= t < 2^23,
+        // t + 2^23 rounded down leaves floor(t) in the mantissa
+        const float t = __fadd_rn(fabsf(s), 0.5f);
+        const int mag = __float_as_int(__fadd_rd(t, 8388608.0f)) & 0x7FFFFF;
+        const int c = s < 0.0f ? -mag : mag;
+        if constexpr (sizeof(E) == 1) o[0] |= (uint32_t)(c & 0xff) << (8 * i);
+        else o[i >> 1] |= (uint32_t)(c & 0xffff) << (16 * (i & 1));
+      }
+      store4raw(ecc, b[hf], n, vec, o);
+    }
   }
 }
 
@@ -296,12 +402,15 @@ __global__ void __launch_bounds__(kQThreads) maxabs_kernel(const T* __restrict__
   if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(a));
 }
 
-// Grid: a persistent loop over 16 CTAs per SM (the SM count is read once per device), never
-// more than the work.  One unit per thread over the whole grid, like the reference's
-// one-block-per-1024-elements launches, was measured too: slower for three of the four
-// master-weight kernels (-DFO_QUANT_BLOCKS_PER_SM=k changes the factor for tuning builds).
+// Grid: a grid-stride loop over at most 128 CTAs per SM (the SM count is read once per device),
+// never more than the work.  Measured on B200 with 2^28 elements: a grid of exactly the
+// resident CTAs (one round, equal shares) was 10 % slower for the quantiser, because the SMs do
+// not all run at the same pace and a fixed share per CTA waits for the slowest; 16 per SM lost
+// to round quantisation (2.7-3.2 rounds at a residency of 5-6); 24 / 32 / 48 / 128 per SM got
+// faster in that order; one unit per thread over the whole grid (no loop) was slower again for
+// five of the seven kernels.  -DFO_QUANT_BLOCKS_PER_SM=k changes the factor for tuning builds.
 #ifndef FO_QUANT_BLOCKS_PER_SM
-#define FO_QUANT_BLOCKS_PER_SM 16
+#define FO_QUANT_BLOCKS_PER_SM 128
 #endif
 static int blocks_for(int64_t units) {
   static int sms[64];
@@ -322,15 +431,18 @@ static int blocks_for(int64_t units) {
   if (b < 1) b = 1;
   return (int)b;
 }
+template <auto kKernel, typename... Args>
+static void launch_strided(int64_t units, cudaStream_t st, Args... args) {
+  kKernel<<<blocks_for(units), kQThreads, 0, st>>>(args...);
+}
 
 template <typename T, bool kSigned, bool kSqrt>
 static void launch_quant(const void* x, void* q, void* scales, int64_t n, int softsign, cudaStream_t st) {
   const int64_t n_units = ((n + kGroup - 1) / kGroup) * (kGroup / kUnit);
-  const int grid = blocks_for(n_units);
   if (softsign)
-    quantize_kernel<T, kSigned, kSqrt, true><<<grid, kQThreads, 0, st>>>((const T*)x, (uint8_t*)q, (__half*)scales, n);
+    launch_strided<quantize_kernel<T, kSigned, kSqrt, true>>(n_units, st, (const T*)x, (uint8_t*)q, (__half*)scales, n);
   else
-    quantize_kernel<T, kSigned, kSqrt, false><<<grid, kQThreads, 0, st>>>((const T*)x, (uint8_t*)q, (__half*)scales, n);
+    launch_strided<quantize_kernel<T, kSigned, kSqrt, false>>(n_units, st, (const T*)x, (uint8_t*)q, (__half*)scales, n);
 }
 template <typename T>
 static void launch_quant_t(const void* x, void* q, void* scales, int64_t n, int is_signed, int do_sqrt,
@@ -347,11 +459,25 @@ static void launch_quant_t(const void* x, void* q, void* scales, int64_t n, int 
 template <bool kSigned, bool kSqrt>
 static void launch_dequant(const void* q, const void* scales, float* out, int64_t n, int softsign,
                            cudaStream_t st) {
-  const int grid = blocks_for((n + kUnit - 1) / kUnit);
+  const int64_t n_units = (n + kUnit - 1) / kUnit;
   if (softsign)
-    dequantize_kernel<kSigned, kSqrt, true><<<grid, kQThreads, 0, st>>>((const uint8_t*)q, (const __half*)scales, out, n);
+    launch_strided<dequantize_kernel<kSigned, kSqrt, true>>(n_units, st, (const uint8_t*)q, (const __half*)scales, out, n);
   else
-    dequantize_kernel<kSigned, kSqrt, false><<<grid, kQThreads, 0, st>>>((const uint8_t*)q, (const __half*)scales, out, n);
+    launch_strided<dequantize_kernel<kSigned, kSqrt, false>>(n_units, st, (const uint8_t*)q, (const __half*)scales, out, n);
+}
+
+// The split / merge kernels take 8 elements per thread and iteration as well (two quads).
+template <typename T, typename E>
+static void launch_decode(const void* narrow, const void* ecc, float* out, int64_t n, cudaStream_t st) {
+  launch_strided<ecc_decode_kernel<T, E>>((n + kUnit - 1) / kUnit, st, (const T*)narrow, (const E*)ecc, out, n);
+}
+template <typename T, typename E>
+static void launch_encode(const float* x, const void* narrow, void* ecc, int64_t n, cudaStream_t st) {
+  launch_strided<ecc_encode_kernel<T, E>>((n + kUnit - 1) / kUnit, st, x, (const T*)narrow, (E*)ecc, n);
+}
+template <typename T>
+static void launch_maxabs(const void* x, int64_t n, float* out, cudaStream_t st) {
+  launch_strided<maxabs_kernel<T>>((n + kUnit - 1) / kUnit, st, (const T*)x, n, out);
 }
 
 }  // namespace fo
@@ -387,17 +513,11 @@ extern "C" int fo_ecc_decode(const void* narrow, int dtype, const void* ecc, int
                              int64_t n, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = fo::blocks_for((n + fo::kUnit - 1) / fo::kUnit);
-  if (dtype == FO_BF16 && err_bytes == 1)
-    fo::ecc_decode_kernel<<<grid, fo::kQThreads, 0, st>>>((const __nv_bfloat16*)narrow, (const int8_t*)ecc, out, n);
-  else if (dtype == FO_BF16 && err_bytes == 2)
-    fo::ecc_decode_kernel<<<grid, fo::kQThreads, 0, st>>>((const __nv_bfloat16*)narrow, (const int16_t*)ecc, out, n);
-  else if (dtype == FO_FP16 && err_bytes == 1)
-    fo::ecc_decode_kernel<<<grid, fo::kQThreads, 0, st>>>((const __half*)narrow, (const int8_t*)ecc, out, n);
-  else if (dtype == FO_FP16 && err_bytes == 2)
-    fo::ecc_decode_kernel<<<grid, fo::kQThreads, 0, st>>>((const __half*)narrow, (const int16_t*)ecc, out, n);
-  else
-    return (int)cudaErrorInvalidValue;
+  if (dtype == FO_BF16 && err_bytes == 1) fo::launch_decode<__nv_bfloat16, int8_t>(narrow, ecc, out, n, st);
+  else if (dtype == FO_BF16 && err_bytes == 2) fo::launch_decode<__nv_bfloat16, int16_t>(narrow, ecc, out, n, st);
+  else if (dtype == FO_FP16 && err_bytes == 1) fo::launch_decode<__half, int8_t>(narrow, ecc, out, n, st);
+  else if (dtype == FO_FP16 && err_bytes == 2) fo::launch_decode<__half, int16_t>(narrow, ecc, out, n, st);
+  else return (int)cudaErrorInvalidValue;
   return (int)cudaGetLastError();
 }
 
@@ -405,28 +525,21 @@ extern "C" int fo_ecc_encode(const float* x, const void* narrow, int dtype, void
                              int64_t n, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = fo::blocks_for((n + fo::kUnit - 1) / fo::kUnit);
-  if (dtype == FO_BF16 && err_bytes == 1)
-    fo::ecc_encode_kernel<<<grid, fo::kQThreads, 0, st>>>(x, (const __nv_bfloat16*)narrow, (int8_t*)ecc, n);
-  else if (dtype == FO_BF16 && err_bytes == 2)
-    fo::ecc_encode_kernel<<<grid, fo::kQThreads, 0, st>>>(x, (const __nv_bfloat16*)narrow, (int16_t*)ecc, n);
-  else if (dtype == FO_FP16 && err_bytes == 1)
-    fo::ecc_encode_kernel<<<grid, fo::kQThreads, 0, st>>>(x, (const __half*)narrow, (int8_t*)ecc, n);
-  else if (dtype == FO_FP16 && err_bytes == 2)
-    fo::ecc_encode_kernel<<<grid, fo::kQThreads, 0, st>>>(x, (const __half*)narrow, (int16_t*)ecc, n);
-  else
-    return (int)cudaErrorInvalidValue;
+  if (dtype == FO_BF16 && err_bytes == 1) fo::launch_encode<__nv_bfloat16, int8_t>(x, narrow, ecc, n, st);
+  else if (dtype == FO_BF16 && err_bytes == 2) fo::launch_encode<__nv_bfloat16, int16_t>(x, narrow, ecc, n, st);
+  else if (dtype == FO_FP16 && err_bytes == 1) fo::launch_encode<__half, int8_t>(x, narrow, ecc, n, st);
+  else if (dtype == FO_FP16 && err_bytes == 2) fo::launch_encode<__half, int16_t>(x, narrow, ecc, n, st);
+  else return (int)cudaErrorInvalidValue;
   return (int)cudaGetLastError();
 }
 
 extern "C" int fo_maxabs(const void* x, int dtype, int64_t n, float* out, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = fo::blocks_for((n + 7) / 8);
   switch (dtype) {
-    case FO_BF16: fo::maxabs_kernel<<<grid, fo::kQThreads, 0, st>>>((const __nv_bfloat16*)x, n, out); break;
-    case FO_FP16: fo::maxabs_kernel<<<grid, fo::kQThreads, 0, st>>>((const __half*)x, n, out); break;
-    case FO_FP32: fo::maxabs_kernel<<<grid, fo::kQThreads, 0, st>>>((const float*)x, n, out); break;
+    case FO_BF16: fo::launch_maxabs<__nv_bfloat16>(x, n, out, st); break;
+    case FO_FP16: fo::launch_maxabs<__half>(x, n, out, st); break;
+    case FO_FP32: fo::launch_maxabs<float>(x, n, out, st); break;
     default: return (int)cudaErrorInvalidValue;
   }
   return (int)cudaGetLastError();

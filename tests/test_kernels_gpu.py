@@ -84,6 +84,52 @@ def test_ecc_decode_every_code_value_bitwise(dtype, code_dtype):
     assert torch.equal(got, oracle.ecc_decode_ref(w, e))
 
 
+@pytest.mark.parametrize("off", [1, 3, 4, 8])
+@pytest.mark.parametrize("n", [7, 250, 4099])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("err_bytes", [1, 2])
+def test_ecc_kernels_on_offset_views(off, n, dtype, err_bytes):
+    """Inputs and outputs that start `off` elements into their buffers (no, 4-, 8- or 16-byte
+    alignment depending on the element size) take the element-wise or the narrower vector
+    paths: same bits as the oracle, and nothing written outside the view."""
+    lib = native.load()
+    st = native.stream_ptr(torch.device("cuda", 0))
+    x = _rand(n + off, torch.float32, 0.05)[off:]
+    w = _rand(n + off, dtype, 1.0)[off:]
+    w.copy_(x.to(dtype))
+    code_dtype = torch.int8 if err_bytes == 1 else torch.int16
+    e_buf = torch.full((n + off + 9,), 77, dtype=code_dtype, device="cuda")
+    rc = lib.fo_ecc_encode(x.data_ptr(), w.data_ptr(), native.DTYPE_CODE[dtype], e_buf[off:].data_ptr(), err_bytes, n, st)
+    assert rc == 0
+    e_ref = oracle.ecc_encode_ref(x.cpu(), w.cpu(), err_bytes)
+    assert torch.equal(e_buf[off:off + n].cpu(), e_ref)
+    assert (e_buf[:off] == 77).all() and (e_buf[off + n:] == 77).all()
+    r_buf = torch.full((n + off + 9,), -5.0, dtype=torch.float32, device="cuda")
+    rc = lib.fo_ecc_decode(w.data_ptr(), native.DTYPE_CODE[dtype], e_buf[off:].data_ptr(), err_bytes,
+                           r_buf[off:].data_ptr(), n, st)
+    assert rc == 0
+    assert torch.equal(r_buf[off:off + n].cpu(), oracle.ecc_decode_ref(w.cpu(), e_ref))
+    assert (r_buf[:off] == -5.0).all() and (r_buf[off + n:] == -5.0).all()
+
+
+@pytest.mark.parametrize("off", [1, 4, 8])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_quantize_on_offset_views(off, dtype):
+    """fp32 input 16 bytes into its buffer uses two 16-byte loads per unit instead of one
+    32-byte load; odd offsets go element by element; the fp32 output likewise."""
+    n = 4099
+    x = _rand(n + off, dtype, 3e-3)[off:]
+    q_buf = torch.full((n + off + 40,), 99, dtype=torch.int8, device="cuda")
+    q, s = quantize(x, out_int8=q_buf[off:off + n], signed=True, sqrt=False, softsign=True)
+    q_ref, s_ref = oracle.quantize_ref(x.cpu(), signed=True, sqrt=False, softsign=True)
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref)
+    assert (q_buf[:off] == 99).all() and (q_buf[off + n:] == 99).all()
+    d_buf = torch.full((n + off + 40,), -5.0, dtype=torch.float32, device="cuda")
+    d = dequantize(q, s, out_float=d_buf[off:off + n], signed=True, sqrt=False, softsign=True)
+    assert torch.equal(d.cpu(), oracle.dequantize_ref(q_ref, s_ref, signed=True, sqrt=False, softsign=True))
+    assert (d_buf[:off] == -5.0).all() and (d_buf[off + n:] == -5.0).all()
+
+
 def test_maxabs():
     x = _rand(100003, torch.bfloat16, 2.0)
     assert maxabs(x) == float(x.abs().max())
