@@ -75,6 +75,11 @@ int fo_step_grid(int device);
 // register-path kernels (which also serve every other combination).
 void fo_set_step_variant(int variant);
 int fo_get_step_variant(void);
+// Grid of the staged kernels = resident CTAs x rounds (1..1024): with more than one round the
+// hardware hands out the later CTAs as earlier ones finish, which evens out SMs that run at
+// different paces.  A tuning knob; the built-in default is what measured best.
+void fo_set_staged_rounds(int rounds);
+int fo_get_staged_rounds(void);
 // Optional: a zeroed device uint32 (of the current device) in which a kernel sets a bit
 // when one of its bounded waits ran out (1: producer, 2: consumer of the staged kernels).
 int fo_set_step_status(void* device_word);

@@ -188,14 +188,30 @@ __global__ void __launch_bounds__(kStagedThreads, StageConfig<kErr>::kCtasPerSm)
   staged_body<T, kErr, 1>(P, H, MomentumUpdate());
 }
 
+// Grid = resident CTAs x up to this factor: the hardware hands out the later CTAs as earlier
+// ones finish, which evens out SMs that run at different paces (equal fixed shares wait for
+// the slowest).  On the 291-tensor Llama-3-8B list, sustained under the power cap: AdamW-24
+// 2.30 -> 2.24 ms per 1 B parameters, AdamW-32 2.54 -> 2.40, Lion-24 1.83 -> 1.78 for a factor of
+// 6-12; 32 loses part of it again.  A CTA keeps at least kMinChunksPerCta chunks so that its
+// ring fills: launches below about 60 M elements keep one round.
+#ifndef FO_STAGED_ROUNDS
+#define FO_STAGED_ROUNDS 8
+#endif
+static int g_staged_rounds = FO_STAGED_ROUNDS;
+constexpr int kMinChunksPerCta = 16;
+
 template <int kErr, int kStates, typename Kernel, typename Hyper>
 static int launch_staged(Kernel kernel, const StepParams& P, const Hyper& H, int sm_count, cudaStream_t st) {
   constexpr int smem_bytes = StageConfig<kErr>::kStages * StageLayout<kErr, kStates>::kStride;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return (int)e;
-  int grid = sm_count * StageConfig<kErr>::kCtasPerSm;
+  const int64_t resident = (int64_t)sm_count * StageConfig<kErr>::kCtasPerSm;
+  int64_t rounds = P.total_chunks / (resident * kMinChunksPerCta);
+  if (rounds > g_staged_rounds) rounds = g_staged_rounds;
+  if (rounds < 1) rounds = 1;
+  int64_t grid = resident * rounds;
   if (P.total_chunks < grid) grid = P.total_chunks;
-  kernel<<<grid, kStagedThreads, smem_bytes, st>>>(P, H);
+  kernel<<<(int)grid, kStagedThreads, smem_bytes, st>>>(P, H);
   return (int)cudaGetLastError();
 }
 
@@ -235,3 +251,7 @@ int staged_momentum_launch(const StepParams& P, const FoMomentumHyper& H, int dt
 }
 
 }  // namespace fo
+
+extern "C" void fo_set_staged_rounds(int rounds) { fo::g_staged_rounds = rounds < 1 ? 1 : (rounds > 1024 ? 1024 : rounds); }
+extern "C" int fo_get_staged_rounds(void) { return fo::g_staged_rounds; }
+

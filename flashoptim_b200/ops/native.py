@@ -114,6 +114,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.fo_chunk_elems.argtypes = []
     lib.fo_step_grid.restype = c_int
     lib.fo_step_grid.argtypes = [c_int]
+    lib.fo_set_staged_rounds.restype = None
+    lib.fo_set_staged_rounds.argtypes = [c_int]
+    lib.fo_get_staged_rounds.restype = c_int
+    lib.fo_get_staged_rounds.argtypes = []
     lib.fo_set_step_variant.restype = None
     lib.fo_set_step_variant.argtypes = [c_int]
     lib.fo_get_step_variant.restype = c_int
