@@ -114,6 +114,15 @@ def set_step_variant(variant: int) -> None:
     native.load().fo_set_step_variant(int(variant))
 
 
+def set_staged_rounds(rounds: int) -> int:
+    """Tuning knob of the staged kernels: their grid is the resident CTAs times up to ``rounds``
+    (1..1024; large launches only).  Returns the previous value."""
+    lib = native.load()
+    old = int(lib.fo_get_staged_rounds())
+    lib.fo_set_staged_rounds(int(rounds))
+    return old
+
+
 
 @dataclass
 class AdamHyper:

@@ -283,6 +283,48 @@ def test_fused_adam_multi_tensor_table(unaligned):
     assert table.uploads == 1
 
 
+@pytest.mark.parametrize("kind", ["adam", "lion"])
+def test_large_launch_grid_rounds_give_the_same_bits(kind):
+    """A launch large enough for the staged kernels to use more CTAs than are resident (several
+    rounds of CTAs, each striding over the chunks) must produce exactly what one round produces:
+    every chunk updated once, none twice.  Two tensors, the second one odd-sized."""
+    from flashoptim_b200.ops.step import set_staged_rounds
+
+    sm = torch.cuda.get_device_properties(0).multi_processor_count
+    chunk = native.load().fo_chunk_elems()
+    sizes = [sm * 3 * 16 * 3 * chunk + 12345, 100003]   # > 2 rounds' worth of chunks at 16 per CTA
+    dtype, err = torch.bfloat16, 1
+    outs = []
+    for rounds in (1, 8):
+        old = set_staged_rounds(rounds)
+        try:
+            ps = [_rand(n, dtype, 0.02, 7 + i) for i, n in enumerate(sizes)]
+            gs = [_rand(n, dtype, 1e-3, 17 + i) for i, n in enumerate(sizes)]
+            es = [torch.zeros(n, dtype=torch.int8, device="cuda") for n in sizes]
+            ms = [torch.zeros(n, dtype=torch.int8, device="cuda") for n in sizes]
+            mss = [torch.zeros(oracle.num_groups(n), dtype=torch.float16, device="cuda") for n in sizes]
+            vs = [torch.zeros(n, dtype=torch.uint8, device="cuda") for n in sizes]
+            vss = [torch.zeros(oracle.num_groups(n), dtype=torch.float16, device="cuda") for n in sizes]
+            table = SegmentTable(torch.device("cuda", torch.cuda.current_device()))
+            for step in (1, 2):
+                if kind == "adam":
+                    rows = make_rows(ps, gs, es, ms, mss, vs, vss)
+                    launch_adam(table, rows, dtype, err, True,
+                                AdamHyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=1e-5, step=step,
+                                          decoupled=True))
+                else:
+                    rows = make_rows(ps, gs, es, ms, mss, [None] * len(sizes), [None] * len(sizes))
+                    launch_momentum(table, rows, dtype, err, native.FO_STATE_Q8,
+                                    MomentumHyper(lr=1e-4, mom_coef=0.99, update_coef=0.9, weight_decay=1e-6, lion=True))
+            torch.cuda.synchronize()
+            outs.append([t.clone() for group in (ps, es, ms, mss, vs, vss) for t in group])
+        finally:
+            set_staged_rounds(old)
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    assert not torch.equal(outs[0][0], _rand(sizes[0], dtype, 0.02, 7))   # the step did change the parameters
+
+
 def test_fused_step_respects_buffer_bounds():
     """Elements outside [0, n) of every stream keep their canary values."""
     n, pad = 1000, 64
