@@ -1,4 +1,4 @@
-"""Host-side logic of the copy-engine paths of the fused FSDP2 integration, on two gloo ranks.
+"""Host-side logic of the copy-engine paths of the fused FSDP2 integration, on two and three gloo ranks.
 
 ``FusedReduceScatter._pull_rows`` / ``_finish_copy_engine`` and the copy-engine branch of
 ``PeerAllGather`` compute source and destination addresses in the ranks' symmetric buffers
@@ -18,7 +18,7 @@ import torch.nn as nn
 
 from dist_utils import run_distributed
 from helpers import check_similar, get_tolerances
-from test_fused_fsdp_wiring_cpu import _FakePeers, _fake_step_from_peers, _net
+from test_fused_fsdp_wiring_cpu import _FakePeers, _fake_step_from_peers
 
 _RANK_SHIFT, _BUF_SHIFT = 48, 32
 
@@ -126,7 +126,8 @@ def _fake_step_local_rows(opt, params, slot):
     for p, pl in zip(params, locals_):
         off = (slot.offsets[id(pl)] - slot.grad_out_sub) // esize
         g = mine[off:off + pl.numel()].view(pl.shape)
-        p.grad = DTensor.from_local(g, p.device_mesh, p.placements, run_check=False) if hasattr(p, "device_mesh") else g
+        p.grad = (DTensor.from_local(g, p.device_mesh, p.placements, run_check=False, shape=p.shape, stride=p.stride())
+                  if hasattr(p, "device_mesh") else g)
     index_of = {id(p): gi for gi, g in enumerate(opt.param_groups) for p in g["params"]}
     for p in params:
         opt._step_group([p], opt.param_groups[index_of[id(p)]], index_of[id(p)])
@@ -136,6 +137,18 @@ def _fake_step_local_rows(opt, params, slot):
         for pl in locals_:
             off = (slot.offsets[id(pl)] - slot.grad_out_sub) // esize
             own[off:off + pl.numel()] = pl.reshape(-1)
+
+
+def _net(world):
+    """Layer sizes that give every rank a 16-byte multiple per group (the copy-engine all-gather's
+    condition), except the last Linear, whose 8 output rows also shard unevenly over 3 ranks."""
+    from flashoptim_b200 import cast_model
+
+    torch.manual_seed(0)
+    d = 8 * world
+    m = nn.Sequential(nn.Linear(d, 2 * d), nn.GELU(), nn.Linear(2 * d, d), nn.LayerNorm(d), nn.Linear(d, 8))
+    cast_model(m, torch.bfloat16)
+    return m
 
 
 def _worker(rank, world):
@@ -163,7 +176,7 @@ def _worker(rank, world):
         return run
 
     g = torch.Generator().manual_seed(5)
-    data = [(torch.randn(world * 4, 16, generator=g), torch.randint(0, 8, (world * 4,), generator=g))
+    data = [(torch.randn(world * 4, 8 * world, generator=g), torch.randint(0, 8, (world * 4,), generator=g))
             for _ in range(4)]
     tol = get_tolerances(torch.bfloat16, True)
     configs = [
@@ -176,7 +189,7 @@ def _worker(rank, world):
     for tag, kwargs in configs:
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")
-            plain, fused = shard(_net()), shard(_net())
+            plain, fused = shard(_net(world)), shard(_net(world))
             o1 = FlashAdamW(plain.parameters(), lr=5e-4)
             o2 = FlashAdamW(fused.parameters(), lr=5e-4)
         o2.step_from_peers = step_fn(o2)
@@ -196,7 +209,7 @@ def _worker(rank, world):
             errors.append(f"{tag}: {state.fused_calls} fused reduce-scatters, {state.fallbacks} fall-backs")
         ce_transport = kwargs.get("transport") == "copy_engine"
         if kwargs.get("all_gather_copy_engine"):
-            # the last Linear's shard (136 bytes per rank) is not a multiple of 16 bytes: NCCL-style fall-back
+            # the last Linear's shard is not a multiple of 16 bytes per rank: NCCL-style fall-back
             if state.ag_calls == 0 or state.ag_fallbacks == 0:
                 errors.append(f"{tag}: {state.ag_calls} copy-engine all-gathers, {state.ag_fallbacks} fall-backs")
         if kwargs.get("push_params"):
@@ -217,5 +230,10 @@ def _worker(rank, world):
     return errors
 
 
-def test_copy_engine_paths_on_gloo():
-    run_distributed(_worker, world_size=2, backend="gloo")
+import pytest
+
+
+@pytest.mark.parametrize("world_size", [2, 3])
+def test_copy_engine_paths_on_gloo(world_size):
+    """Three ranks: uneven (padded) shards and a ring of more than one peer per rank."""
+    run_distributed(_worker, world_size=world_size, backend="gloo")

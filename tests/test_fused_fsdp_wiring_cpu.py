@@ -75,7 +75,8 @@ def _fake_step_from_peers(opt, params, slot):
     for p, pl in zip(params, locals_):
         off = (slot.offsets[id(pl)] - slot.grad_out_sub) // esize
         g = mine[off:off + pl.numel()].view(pl.shape)
-        p.grad = DTensor.from_local(g, p.device_mesh, p.placements, run_check=False) if hasattr(p, "device_mesh") else g
+        p.grad = (DTensor.from_local(g, p.device_mesh, p.placements, run_check=False, shape=p.shape, stride=p.stride())
+                  if hasattr(p, "device_mesh") else g)
     index_of = {id(p): gi for gi, g in enumerate(opt.param_groups) for p in g["params"]}
     for p in params:
         opt._step_group([p], opt.param_groups[index_of[id(p)]], index_of[id(p)])
