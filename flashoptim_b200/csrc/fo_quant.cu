@@ -1,6 +1,7 @@
 // Stand-alone group quantiser / dequantiser, master-weight split and maxabs.
 //
-// These run at state creation, checkpoint save/load and fp32 export/import, so
+// These run at checkpoint save/load, fp32 export/import and when a state is set
+// from a full-precision tensor (never inside a training step), so
 // they use exact IEEE arithmetic (explicit round-to-nearest intrinsics, which
 // the compiler never contracts into FMAs) and reproduce the PyTorch formulation
 // in ops/oracle.py bit for bit.  What they compute matches
