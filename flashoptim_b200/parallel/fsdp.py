@@ -34,18 +34,16 @@ without gradients) fall back to NCCL for that call.
 
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from ..ops import native
 from ..optim.base import FlashOptimizer, local_tensor
 from .symm import ParamPush, PeerGradients, PeerGroup
-
-import ctypes
-
-from ..ops import native
 
 try:  # torch >= 2.8
     from torch.distributed.fsdp import FSDPModule
@@ -164,7 +162,6 @@ class FusedReduceScatter(ReduceScatter):  # type: ignore[misc,valid-type]
                 self.gather.invalidate()
         self.ctx.fused_calls += 1
         return None
-
 
     # ---- copy-engine transport: the bytes cross NVLink in cudaMemcpyAsync copies (no SM), the
     # update kernel reads local memory only and runs at HBM speed
