@@ -84,7 +84,7 @@ def time_fn(fn, iters: int, warmup: int) -> float:
 
 
 def run_kernels(args, peak: float, peak_src: str) -> list[dict]:
-    """Stand-alone kernels on 2^28 elements (0.5 GB of bf16: far beyond the 126 MB L2)."""
+    """Stand-alone kernels on 2^28 elements by default (0.5 GB of bf16: far beyond the 126 MB L2)."""
     dev = torch.device("cuda", 0)
     if args.impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
@@ -93,7 +93,7 @@ def run_kernels(args, peak: float, peak_src: str) -> list[dict]:
     else:
         import flashoptim_b200 as lib
         from flashoptim_b200 import dequantize, quantize
-    n = 1 << 28
+    n = 1 << args.log2_elems
     g = torch.Generator(device=dev).manual_seed(0)
     x32 = torch.empty(n, device=dev).normal_(0, 0.02, generator=g)
     xb = x32.to(torch.bfloat16)
@@ -156,6 +156,8 @@ def main() -> None:
     ap.add_argument("--variant", type=int, default=None, help="ours: 0 register-path kernels, 1 staged (default)")
     ap.add_argument("--kernels", action="store_true",
                     help="time the stand-alone quantise / dequantise / master-weight split kernels instead")
+    ap.add_argument("--log2-elems", type=int, default=28,
+                    help="--kernels: tensor size as a power of two (26 for a profiler capture: 256 MB of fp32)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
 

@@ -240,6 +240,32 @@ __device__ __forceinline__ float narrow_bits_to_float(uint16_t bits) {
   else return __uint_as_float((uint32_t)bits << 16);
 }
 
+// 2^ls and 2^-ls (ls = E(w) - M - 1) as single floats, straight from the exponent field of the
+// narrow value.  The PyTorch formulation scales by two powers of two so that nothing under- or
+// overflows on the way; one factor gives the same bits whenever it is itself a normal number and
+// the scaled correction is (an exact scaling then, and `code * 2^ls + w` rounds once either
+// way).  fp16: always (E >= -14; subnormals and zero share the smallest normal's exponent, the
+// clamp).  bf16: for |w| >= 2^-94; smaller values, zero included, take the two-factor form.
+template <typename T>
+__device__ __forceinline__ bool single_scale_ok(float w) {
+  if constexpr (std::is_same<T, __half>::value) return true;
+  else return fabsf(w) >= 5.048709793414476e-29f;  // 2^-94; false for NaN
+}
+template <typename T>
+__device__ __forceinline__ float ecc_scale(uint16_t bits) {
+  if constexpr (std::is_same<T, __half>::value)
+    return __uint_as_float((max((uint32_t)bits & 0x7C00u, 0x0400u) << 13) + ((127u - 15u - 11u) << 23));
+  else
+    return __uint_as_float((((uint32_t)bits << 16) & 0x7F800000u) - (8u << 23));
+}
+template <typename T>
+__device__ __forceinline__ float ecc_inv_scale(uint16_t bits) {
+  if constexpr (std::is_same<T, __half>::value)
+    return __uint_as_float(((127u + 15u + 11u) << 23) - (max((uint32_t)bits & 0x7C00u, 0x0400u) << 13));
+  else
+    return __uint_as_float(((254u + 8u) << 23) - (((uint32_t)bits << 16) & 0x7F800000u));
+}
+
 // The split / merge kernels use an interleaved layout: a warp owns a tile of 256 consecutive
 // elements and a lane moves elements [4 * lane, 4 * lane + 4) of each half, so that every
 // warp-wide access covers one contiguous span (512 / 256 / 128 bytes for 4- / 2- / 1-byte
@@ -328,14 +354,30 @@ __global__ void __launch_bounds__(kQThreads, kEccMinBlocks)
 #pragma unroll
       for (int k = 0; k < (int)sizeof(E); ++k) wc[hf][k] ^= flip;
       uint32_t r[4];
+      uint16_t hb[4];
+      float wf[4];
+      bool single = true;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint16_t hb = (uint16_t)(wn[hf][i >> 1] >> (16 * (i & 1)));
-        const int ls = ecc_log_scale_bits<T>(hb);
-        const int hh = ls >> 1;  // floor(ls / 2)
-        const float corr = div_by_code_range(quad_code_f<E>(wc[hf], i), smax);
-        const float e = __fmul_rn(__fmul_rn(corr, pow2i(hh)), pow2i(ls - hh));
-        r[i] = __float_as_uint(__fadd_rn(narrow_bits_to_float<T>(hb), e));
+        hb[i] = (uint16_t)(wn[hf][i >> 1] >> (16 * (i & 1)));
+        wf[i] = narrow_bits_to_float<T>(hb[i]);
+        single = single && single_scale_ok<T>(wf[i]);
+      }
+      if (single) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float corr = div_by_code_range(quad_code_f<E>(wc[hf], i), smax);
+          r[i] = __float_as_uint(__fmaf_rn(corr, ecc_scale<T>(hb[i]), wf[i]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int ls = ecc_log_scale_bits<T>(hb[i]);
+          const int hh = ls >> 1;  // floor(ls / 2)
+          const float corr = div_by_code_range(quad_code_f<E>(wc[hf], i), smax);
+          const float e = __fmul_rn(__fmul_rn(corr, pow2i(hh)), pow2i(ls - hh));
+          r[i] = __float_as_uint(__fadd_rn(wf[i], e));
+        }
       }
       store4raw(out, b[hf], n, vec, r);
     }
@@ -363,13 +405,26 @@ __global__ void __launch_bounds__(kQThreads, kEccMinBlocks)
       uint32_t o[sizeof(E)];
 #pragma unroll
       for (int k = 0; k < (int)sizeof(E); ++k) o[k] = 0;
+      uint16_t hb[4];
+      float wf[4];
+      bool single = true;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint16_t hb = (uint16_t)(wn[hf][i >> 1] >> (16 * (i & 1)));
-        const int neg = -ecc_log_scale_bits<T>(hb);
-        const int hh = neg >> 1;
-        const float e = __fsub_rn(__uint_as_float(wx[hf][i]), narrow_bits_to_float<T>(hb));
-        float en = __fmul_rn(__fmul_rn(e, pow2i(hh)), pow2i(neg - hh));
+        hb[i] = (uint16_t)(wn[hf][i >> 1] >> (16 * (i & 1)));
+        wf[i] = narrow_bits_to_float<T>(hb[i]);
+        single = single && single_scale_ok<T>(wf[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float e = __fsub_rn(__uint_as_float(wx[hf][i]), wf[i]);
+        float en;
+        if (single) {
+          en = __fmul_rn(e, ecc_inv_scale<T>(hb[i]));
+        } else {
+          const int neg = -ecc_log_scale_bits<T>(hb[i]);
+          const int hh = neg >> 1;
+          en = __fmul_rn(__fmul_rn(e, pow2i(hh)), pow2i(neg - hh));
+        }
         en = fminf(fmaxf(en, -1.0f), 1.0f);  // a NaN difference becomes -1
         const float s = __fmul_rn(en, smax);
         // copysign(floor(|s| + 0.5), s) without a float-to-int conversion: for 0 <= t < 2^23,

@@ -36,11 +36,21 @@ def test_ecc_invariants_all_mantissas(dtype, fields, sign):
     assert not bad, bad
 
 
-def test_cuda_codes_equal_the_cpu_formulation_on_a_full_binade():
+@pytest.mark.parametrize("dtype,field", [
+    (torch.bfloat16, 120), (torch.bfloat16, 0),
+    # the kernels switch from two scale factors to one at |w| = 2^-94 (bf16): both sides of it
+    (torch.bfloat16, 32), (torch.bfloat16, 33), (torch.bfloat16, 34), (torch.bfloat16, 254),
+    (torch.float16, 118), (torch.float16, 127 - 20), (torch.float16, 127 + 15),
+])
+def test_cuda_codes_equal_the_cpu_formulation_on_a_full_binade(dtype, field):
+    """Split and merge, bit for bit with the PyTorch formulation, over all 2^23 mantissas of one
+    fp32 exponent (field 0 and fp16 field 107: subnormal narrow values; 254 / 142: the top)."""
     mant = torch.arange(0, 1 << 23, dtype=torch.int32)
-    for dtype, field in ((torch.bfloat16, 120), (torch.float16, 118), (torch.bfloat16, 0)):
-        x = fp32_with_exponent(field, 1, mant)
-        w = x.to(dtype)
-        for mbw in (3, 4):
-            got = compute_ecc_bits(x.cuda(), w.cuda(), master_bytewidth=mbw).cpu()
-            assert torch.equal(got, oracle.ecc_encode_ref(x, w, mbw - 2)), (dtype, field, mbw)
+    x = fp32_with_exponent(field, 1, mant)
+    w = x.to(dtype)
+    for mbw in (3, 4):
+        got = compute_ecc_bits(x.cuda(), w.cuda(), master_bytewidth=mbw)
+        want = oracle.ecc_encode_ref(x, w, mbw - 2)
+        assert torch.equal(got.cpu(), want), (dtype, field, mbw)
+        back = reconstruct_fp32_param(w.cuda(), got).cpu()
+        assert torch.equal(back.view(torch.int32), oracle.ecc_decode_ref(w, want).view(torch.int32)), (dtype, field, mbw)
