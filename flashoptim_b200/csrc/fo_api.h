@@ -1,4 +1,7 @@
-// C ABI of libflashoptim_b200.so.  Every function returns a cudaError_t value
+// C ABI of libflashoptim_b200.so: the launch layer that the reference implements as Python
+// wrappers around Triton kernels (flashoptim/optimizers.py:1535-1583 momentum, :2203-2252 Adam,
+// :2446-2540 quantize / dequantize, :2835-2974 master-weight split / merge).
+// Every function returns a cudaError_t value
 // (0 on success) unless stated otherwise, takes raw device pointers and a CUDA
 // stream handle, launches asynchronously on that stream and allocates nothing.
 #pragma once

@@ -1,5 +1,8 @@
-// Device helpers shared by the kernels that fuse a gradient collective with the update
-// (fo_comm.cu: register path; fo_comm_staged.cu: bulk-copy staged path): epoch flags with
+// Device helpers shared by the kernels that fuse a gradient collective with the update.  No
+// counterpart in the reference, which leaves every collective to DDP / FSDP2 and NCCL and steps
+// afterwards (gradient-release hook: flashoptim/optimizers.py:3019-3051).
+//
+// Used by fo_comm.cu (register path) and fo_comm_staged.cu (bulk-copy staged path): epoch flags with
 // bounded waits, the start barrier / end signal of a kernel, multimem instructions, the
 // walker over a segment table whose gradient entries are byte offsets into symmetric
 // buffers, and the stores that hand the averaged gradient back and push the new parameters.

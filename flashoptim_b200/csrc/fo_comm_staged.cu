@@ -1,5 +1,6 @@
 // Bulk-copy staged variant of the steps fused with the gradient collective (bf16 / fp16
-// parameters, 8-bit states, peer loads).
+// parameters, 8-bit states, peer loads).  No counterpart in the reference (NCCL reduce-scatter,
+// then flashoptim/optimizers.py:2256-2443 per tensor).
 //
 // The register-path kernels of fo_comm.cu keep at most 8 x 16 bytes of remote requests in
 // flight per thread, so saturating NVLink (770 GB/s x a few microseconds of latency = a few

@@ -1,5 +1,10 @@
 // Shared device code for the sm_100a optimizer kernels.
 //
+// Counterparts in the reference (all Triton): group quantise / dequantise inside the step
+// kernels, flashoptim/optimizers.py:2543-2676; exponent and correction-code device functions,
+// :2683-2776.  The forms here are rearranged for instruction count and documented where they
+// deviate in the last bit; the exact forms live in fo_quant.cu.
+//
 // Layout conventions used by every kernel in this library:
 //   * a "unit" is 8 consecutive elements handled by one thread, a quarter of a
 //     32-element quantisation group, so a group is four adjacent lanes and its

@@ -1,5 +1,10 @@
 // Per-unit (8 element) load / update / store of the fused optimizer steps.
 //
+// What a unit goes through equals one program of the reference's _triton_momentum_kernel
+// (flashoptim/optimizers.py:1587-1719: SGD / SGDW / Lion) and _triton_adam_kernel
+// (:2256-2443): rebuild the master value from narrow value + correction code, dequantise the
+// states, update in fp32, requantise, re-split.
+//
 // The same three phases serve the plain multi-tensor step kernels and the
 // kernels that take their gradient from NVLink peers: those replace only the
 // gradient load.

@@ -1,4 +1,6 @@
 // Bulk-copy staged variants of the fused steps (bf16 / fp16 parameters, 8-bit states).
+// Same arithmetic as the reference's step kernels (flashoptim/optimizers.py:1587-1719,
+// :2256-2443); the data path below has no counterpart there.
 //
 // The register-path kernels hold at most 32 warps x 56 B of loads in flight per
 // SM and sit at about one eligible warp per scheduler.  Here a producer warp

@@ -1,4 +1,8 @@
 // Launch configuration, segment table and chunk walker shared by the step kernels.
+//
+// No counterpart in the reference, which launches one Triton kernel per parameter tensor
+// (flashoptim/optimizers.py:1535-1583, :2203-2252; grid from _make_grid, :2984-2996): here one
+// launch walks a table of all tensors of a step.
 #pragma once
 
 #include "fo_step_core.cuh"

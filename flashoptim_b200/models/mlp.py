@@ -1,4 +1,5 @@
-"""784 -> 256 -> ReLU -> 10 classifier: the smallest end-to-end configuration."""
+"""784 -> 256 -> ReLU -> 10 classifier: the smallest end-to-end configuration (the model of the
+reference's only example, ``examples/train_mnist.py``)."""
 
 from __future__ import annotations
 

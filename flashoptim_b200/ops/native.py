@@ -3,6 +3,8 @@
 The library speaks a plain C ABI (``csrc/fo_api.h``): raw device pointers, a
 stream handle, ``cudaError_t`` return codes.  Nothing here falls back to
 PyTorch: if the library cannot be loaded on a CUDA machine the call raises.
+It takes the place of the reference's Triton launch wrappers
+(``flashoptim/optimizers.py:1535-1583``, ``:2203-2252``, ``:2446-2540``, ``:2835-2974``).
 """
 
 from __future__ import annotations

@@ -1,4 +1,10 @@
-"""Helpers shared by the algorithm classes: eager write-back and fused row packing."""
+"""Helpers shared by the algorithm classes: eager write-back and fused row packing.
+
+The reference reaches its kernels per tensor through ``_fused_momentum_step`` /
+``_fused_adam_step`` (``flashoptim/optimizers.py:1535-1583``, ``:2203-2252``) and writes the eager
+result back in ``_do_step`` (``:1280-1345``, ``:1414-1511``, ``:1876-1978``); here the tensors of a
+whole step are packed into one address table first.
+"""
 
 from __future__ import annotations
 
