@@ -17,7 +17,7 @@ the achieved fraction of the measured copy bandwidth (MEASURED_PEAKS.json), plus
 the SM clocks and throttle reasons sampled through NVML (read-only) during the run.
 ``--kernels`` times the stand-alone group quantiser / dequantiser and the master-weight
 split / merge (the reference's Triton kernels ``flashoptim/optimizers.py:2541-2676,
-2779-2832``) on one 2^28-element tensor instead.
+2779-2832``) on one 2^28-element tensor instead (``--log2-elems 26`` for a profiler capture).
 """
 
 from __future__ import annotations
