@@ -227,6 +227,52 @@ def _worker(rank, world):
         if peers.barriers != expect_barriers:
             errors.append(f"{tag}: {peers.barriers} barriers, expected {expect_barriers}")
         state.remove()
+
+    # switching the all-gather between steps (what a comparison run does): push -> copy engines
+    # -> FSDP2's own -> push again; the parameters must follow the plain model throughout and
+    # each mode must be the one that serves the all-gathers
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        plain, fused = shard(_net(world)), shard(_net(world))
+        o1 = FlashAdamW(plain.parameters(), lr=5e-4)
+        o2 = FlashAdamW(fused.parameters(), lr=5e-4)
+    o2.step_from_peers = step_fn(o2)
+    state = fsdp_mod.enable_fused_fsdp(fused, o2, push_params=True, own_all_gather=True, all_gather_copy_engine=True)
+    if state.all_gather_mode != "push":
+        errors.append(f"mode after enabling with push_params: {state.all_gather_mode}")
+    for mode in ("push", "pull", "nccl", "push"):
+        state.set_all_gather_mode(mode)
+        if any(gather.is_current() for gather in state.gathers):
+            errors.append(f"mode {mode}: a push buffer is still marked current right after the switch")
+        before = (state.ag_eliminated, state.ag_calls, state.ag_fallbacks)
+        for step, (x, y) in enumerate(data[:3]):
+            xs, ys = x[rank * 4:(rank + 1) * 4].bfloat16(), y[rank * 4:(rank + 1) * 4]
+            for model, opt in ((plain, o1), (fused, o2)):
+                nn.functional.cross_entropy(model(xs).float(), ys).backward()
+                opt.step()
+                opt.zero_grad()
+            for (n1, p1), (_, p2) in zip(plain.named_parameters(), fused.named_parameters()):
+                errors += check_similar(p2.detach().full_tensor(), p1.detach().full_tensor(), tol,
+                                        f"mode {mode} step {step} {n1}")
+        eliminated, pulled, fell_back = (a - b for a, b in
+                                         zip((state.ag_eliminated, state.ag_calls, state.ag_fallbacks), before))
+        if mode == "push" and (eliminated < 4 * 2 or pulled):
+            errors.append(f"mode push: {eliminated} all-gathers served by pushes, {pulled} by copies")
+        if mode == "pull" and (eliminated or not pulled):
+            errors.append(f"mode pull: {eliminated} all-gathers served by pushes, {pulled} by copies")
+        if mode == "nccl" and (eliminated or pulled):
+            errors.append(f"mode nccl: {eliminated} all-gathers served by pushes, {pulled} by copies")
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        bare = shard(_net(world))
+        o3 = FlashAdamW(bare.parameters(), lr=5e-4)
+    bare_state = fsdp_mod.enable_fused_fsdp(bare, o3)  # neither push buffers nor an all-gather pool
+    for mode in ("push", "pull"):
+        try:
+            bare_state.set_all_gather_mode(mode)
+            errors.append(f"mode {mode} was accepted although its buffers were never allocated")
+        except ValueError:
+            pass
     return errors
 
 
