@@ -24,8 +24,8 @@ hook on unsynchronised backwards and the bucket later holds the accumulated sum.
 
 What it buys, measured (GPT-2 medium, 8 sequences of 1024 per GPU, B200): the fused hook is a
 correctness-complete alternative, NOT a speed-up.  It ran within 1 % of NCCL all-reduce followed
-by this library's multi-tensor step (50.0 vs 49.3 ms per step on 2 GPUs, 50.7 vs 50.2 on 8) and
-5 % ahead of the reference optimizer on stock DDP.  DDP's reducer owns its buckets, so every
+by this library's multi-tensor step (50.0 vs 49.3 ms per step on 2 GPUs, 50.4 vs 49.4 on 4,
+50.7 vs 50.2 on 8) and 5 % ahead of the reference optimizer on stock DDP (52.8 ms on 4 GPUs).  DDP's reducer owns its buckets, so every
 bucket is first copied into the symmetric arena (one more pass of all gradients through HBM),
 and a replicated update is HBM-bound on every rank whatever the collective does.  The fused
 FSDP2 path (``enable_fused_fsdp``), where each rank updates only its shard, is where fusing
