@@ -4,6 +4,11 @@ architectures (the smoke test of the reference's ``test/test_thirdparty.py:271-2
 The reference downloads configurations; here every model is a two-layer,
 32-wide random-init instance built from its Hugging Face config class, so the
 test needs no network and runs on CPU in well under a second per model.
+timm, diffusers and open_clip are not installable offline: torchvision's ResNet
+(batch norm, integer buffers), a Swin (integer ``relative_position_index``), a
+small MLP-Mixer and a two-tower CLIP stand in for the reference's timm and
+open_clip entries (``test/test_thirdparty.py:122-145``, ``:324-366``); its
+diffusers UNet has no stand-in.
 """
 
 import warnings
@@ -85,9 +90,87 @@ def _whisper(t):
     return t.WhisperForConditionalGeneration(cfg), inputs, (lambda out: out.loss)
 
 
+def _square(out):
+    return out.float().pow(2).mean()
+
+
+def _resnet(t):
+    """Stands in for timm's resnet50 (``test/test_thirdparty.py:126``): BatchNorm layers, which
+    ``cast_model`` keeps in fp32, and their integer ``num_batches_tracked`` buffers."""
+    tv = pytest.importorskip("torchvision")
+    return tv.models.resnet18(num_classes=10), dict(x=torch.randn(2, 3, 64, 64).bfloat16()), _square
+
+
+def _swin(t):
+    """timm's swin_tiny (``:128``): an integer ``relative_position_index`` buffer per block."""
+    cfg = t.SwinConfig(image_size=32, patch_size=4, embed_dim=16, depths=[2, 2], num_heads=[2, 4], window_size=4,
+                       num_labels=5)
+    inputs = dict(pixel_values=torch.randn(2, 3, 32, 32).bfloat16(), labels=torch.tensor([1, 2]))
+    return t.SwinForImageClassification(cfg), inputs, (lambda out: out.loss)
+
+
+class _Mixer(torch.nn.Module):
+    """timm's mixer_b16 (``:129``) in miniature: token- and channel-mixing MLPs, no conv, no attention."""
+
+    def __init__(self, patches=16, dim=32, depth=2, classes=10):
+        super().__init__()
+        nn = torch.nn
+        self.embed = nn.Linear(3 * 8 * 8, dim)
+        self.blocks = nn.ModuleList(nn.ModuleDict(dict(
+            n1=nn.LayerNorm(dim), tok=nn.Sequential(nn.Linear(patches, 2 * patches), nn.GELU(), nn.Linear(2 * patches, patches)),
+            n2=nn.LayerNorm(dim), ch=nn.Sequential(nn.Linear(dim, 2 * dim), nn.GELU(), nn.Linear(2 * dim, dim)),
+        )) for _ in range(depth))
+        self.head = nn.Linear(dim, classes)
+
+    def forward(self, x):
+        b = x.shape[0]
+        x = x.unfold(2, 8, 8).unfold(3, 8, 8).permute(0, 2, 3, 1, 4, 5).reshape(b, 16, -1)
+        x = self.embed(x)
+        for blk in self.blocks:
+            x = x + blk["tok"](blk["n1"](x).transpose(1, 2)).transpose(1, 2)
+            x = x + blk["ch"](blk["n2"](x))
+        return self.head(x.mean(1))
+
+
+def _mixer(t):
+    return _Mixer(), dict(x=torch.randn(2, 3, 32, 32).bfloat16()), _square
+
+
+def _clip_dual(t):
+    """Stands in for open_clip's ViT-B-32 (``:324-366``): an image and a text tower with a shared loss."""
+    cfg = t.CLIPConfig(
+        text_config=dict(**_TINY, projection_dim=16),
+        vision_config=dict(hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                           image_size=32, patch_size=8, projection_dim=16),
+        projection_dim=16)
+    inputs = dict(input_ids=_IDS, pixel_values=torch.randn(2, 3, 32, 32).bfloat16(), return_loss=True)
+    return t.CLIPModel(cfg), inputs, (lambda out: out.loss)
+
+
+def _sam(t):
+    cfg = t.SamConfig(
+        vision_config=dict(hidden_size=32, output_channels=16, num_hidden_layers=2, num_attention_heads=4, image_size=64,
+                           patch_size=16, window_size=2, global_attn_indexes=[1], mlp_dim=64, num_pos_feats=8),
+        prompt_encoder_config=dict(hidden_size=16, image_size=64, patch_size=16, mask_input_channels=4),
+        mask_decoder_config=dict(hidden_size=16, mlp_dim=32, num_hidden_layers=1, num_attention_heads=2,
+                                 iou_head_hidden_dim=16))
+    inputs = dict(pixel_values=torch.randn(1, 3, 64, 64).bfloat16(),
+                  input_points=torch.tensor([[[[20.0, 20.0]]]]).bfloat16(), input_labels=torch.tensor([[[1]]]))
+    return t.SamModel(cfg), inputs, (lambda out: out.pred_masks.float().pow(2).mean() + out.iou_scores.float().sum())
+
+
+def _qwen35(t):
+    cfg = t.Qwen3_5Config(text_config=dict(**_TINY, num_key_value_heads=2, head_dim=8, linear_num_value_heads=4,
+                                           linear_num_key_heads=2, linear_key_head_dim=8, linear_value_head_dim=8))
+    inputs, loss_of = _lm()
+    # two layers are both linear-attention layers: no key/value cache to ask for a length
+    return t.Qwen3_5ForCausalLM(cfg.text_config if hasattr(cfg, "text_config") else cfg), dict(inputs, use_cache=False), loss_of
+
+
 _BUILDERS = {
     "gpt2": _gpt2, "bert": _bert, "llama": _llama, "qwen2": _qwen2, "qwen3_moe": _qwen3_moe, "gemma2": _gemma2,
     "mamba": _mamba, "vit": _vit, "dinov2": _dinov2, "clip_text": _clip_text, "whisper": _whisper,
+    "resnet": _resnet, "swin": _swin, "mixer": _mixer, "clip_dual": _clip_dual, "sam": _sam, "qwen3_5": _qwen35,
 }
 
 
@@ -97,14 +180,19 @@ def test_cast_forward_backward_step(name, optimizer):
     torch.manual_seed(0)
     try:
         model, inputs, loss_of = _BUILDERS[name](transformers)
-    except (AttributeError, TypeError) as e:  # architecture or config argument not in this transformers version
+    except (AttributeError, TypeError, ValueError) as e:  # architecture or config argument not in this transformers version
         pytest.skip(f"{name}: {e}")
     shapes = {n: tuple(p.shape) for n, p in model.named_parameters()}
     tied_before = len({id(p) for p in model.parameters()})
+    int_buffers = {n: b.dtype for n, b in model.named_buffers() if not b.dtype.is_floating_point}
+    batch_norms = {id(p) for m in model.modules() if isinstance(m, torch.nn.modules.batchnorm._BatchNorm)
+                   for p in m.parameters()}
     cast_model(model, torch.bfloat16)
     assert {n: tuple(p.shape) for n, p in model.named_parameters()} == shapes
     assert len({id(p) for p in model.parameters()}) == tied_before
-    assert all(p.dtype == torch.bfloat16 for p in model.parameters())
+    # everything narrow except batch-norm parameters, which stay fp32; integer buffers untouched
+    assert all(p.dtype == (torch.float32 if id(p) in batch_norms else torch.bfloat16) for p in model.parameters())
+    assert {n: b.dtype for n, b in model.named_buffers() if not b.dtype.is_floating_point} == int_buffers
     opt = optimizer(model.parameters(), lr=1e-3)
     before = [p.detach().clone() for p in model.parameters()]
     with warnings.catch_warnings():
