@@ -3,7 +3,8 @@ architectures (the smoke test of the reference's ``test/test_thirdparty.py:271-2
 
 The reference downloads configurations; here every model is a two-layer,
 32-wide random-init instance built from its Hugging Face config class, so the
-test needs no network and runs on CPU in well under a second per model.
+test needs no network and runs on CPU in well under a second per model (ten of them once
+more on the GPU, where the CUDA kernels meet these parameter lists).
 timm, diffusers and open_clip are not installable offline: torchvision's ResNet
 (batch norm, integer buffers), a Swin (integer ``relative_position_index``), a
 small MLP-Mixer and a two-tower CLIP stand in for the reference's timm and
@@ -174,14 +175,22 @@ _BUILDERS = {
 }
 
 
-@pytest.mark.parametrize("name", sorted(_BUILDERS))
-@pytest.mark.parametrize("optimizer", [FlashAdamW, FlashLion])
-def test_cast_forward_backward_step(name, optimizer):
+# the architectures that have also been run through the CUDA kernels on a B200 (FlashAdamW); the
+# others have only been run on CPU
+_GPU_NAMES = ["bert", "clip_dual", "clip_text", "dinov2", "gemma2", "gpt2", "llama", "mamba", "mixer", "qwen2"]
+_CASES = [(n, o, "cpu") for o in (FlashAdamW, FlashLion) for n in sorted(_BUILDERS)]
+_CASES += [pytest.param(n, FlashAdamW, "cuda", marks=pytest.mark.gpu) for n in _GPU_NAMES]
+
+
+@pytest.mark.parametrize("name,optimizer,device", _CASES)
+def test_cast_forward_backward_step(name, optimizer, device):
     torch.manual_seed(0)
     try:
         model, inputs, loss_of = _BUILDERS[name](transformers)
     except (AttributeError, TypeError, ValueError) as e:  # architecture or config argument not in this transformers version
         pytest.skip(f"{name}: {e}")
+    model = model.to(device)
+    inputs = {k: v.to(device) if torch.is_tensor(v) else v for k, v in inputs.items()}
     shapes = {n: tuple(p.shape) for n, p in model.named_parameters()}
     tied_before = len({id(p) for p in model.parameters()})
     int_buffers = {n: b.dtype for n, b in model.named_buffers() if not b.dtype.is_floating_point}
