@@ -18,7 +18,7 @@ os.environ.setdefault("FLASHOPTIM_ALLOW_INEFFECTIVE_MASTER_WEIGHT_BITS", "1")
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
     config.addinivalue_line("markers", "multigpu: needs at least two CUDA devices")
-    config.addinivalue_line("markers", "thirdparty: tiny random-init Hugging Face models (CPU, no network)")
+    config.addinivalue_line("markers", "thirdparty: tiny random-init third-party models (no network; CPU, ten of them also on the GPU)")
 
 
 def pytest_collection_modifyitems(config, items):
